@@ -25,9 +25,10 @@ class LayerCache:
     pages: Optional[torch.Tensor]  # [num_pages, planes, kv_heads, page_size, head_dim]
     block_table: Optional[torch.Tensor]  # [requests in step, width] int32
     page_size: int
-    state: Optional[torch.Tensor]  # [max_slots, *state shape]
+    state: object  # the mixer's state: None, [max_slots, *state shape], or a dict name -> such a tensor
     writable: bool
     group: int = -1
+    block_state: object = None  # the block arrangement's own state, in the same forms
 
 
 def plan_groups(needs: list, num_pages: int) -> tuple[list[GroupSpec], dict]:
@@ -70,19 +71,34 @@ class CacheStorage:
             torch.zeros((len(g.entries), g.num_pages, g.planes, g.num_kv_heads, page_size, g.head_dim), device=device, dtype=dtype)
             for g in self.groups
         ]
-        self.states = {}
+        def make(spec):
+            if spec is None:
+                return None
+            if isinstance(spec, dict):
+                return {name: make(one) for name, one in spec.items()}
+            return torch.zeros((max_slots, *spec.slot_shape(max_seq_len)), device=device, dtype=getattr(torch, spec.dtype))
+
+        self.states, self.block_states = {}, {}
         for need in needs:
             if need.state is not None:
-                self.states[need.entry] = torch.zeros((max_slots, *need.state.shape), device=device,
-                                                      dtype=getattr(torch, need.state.dtype))
+                self.states[need.entry] = make(need.state)
+            if getattr(need, "block_state", None) is not None:
+                self.block_states[need.entry] = make(need.block_state)
+
+    def state_tensors(self) -> list:
+        """Every state tensor (of mixers and of block arrangements), flat."""
+        out = []
+        for held in (*self.states.values(), *self.block_states.values()):
+            out += list(held.values()) if isinstance(held, dict) else [held]
+        return out
 
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.pages) + sum(
-            t.numel() * t.element_size() for t in self.states.values())
+            t.numel() * t.element_size() for t in self.state_tensors())
 
     def clear_slot(self, slot: int) -> None:
         """Zero the state rows of a slot (at admission)."""
-        for state in self.states.values():
+        for state in self.state_tensors():
             state[slot].zero_()
 
     def layer_caches(self, block_tables: list) -> list[LayerCache]:
@@ -95,5 +111,6 @@ class CacheStorage:
                 group, layer = self.where[need.owner]
                 pages, table = self.pages[group][layer], block_tables[group]
             out.append(LayerCache(pages, table, self.page_size, self.states.get(need.entry),
-                                  writable=need.owner == need.entry, group=group))
+                                  writable=need.owner == need.entry, group=group,
+                                  block_state=self.block_states.get(need.entry)))
         return out

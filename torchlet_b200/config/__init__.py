@@ -11,10 +11,12 @@ from .spec import LayerSpec, ModelSpec, NormSlot, PartSpec, ScheduleEntry
 from .qwen2 import Qwen2Config
 from .dodonex import DodonexConfig
 from .numuzen import NumuzenConfig
+from .fusolix import FusolixConfig
 
 __all__ = [
     "DodonexConfig",
     "EngineConfig",
+    "FusolixConfig",
     "LayerSpec",
     "ModelSpec",
     "NumuzenConfig",

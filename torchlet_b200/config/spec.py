@@ -96,6 +96,9 @@ class ModelSpec:
     tie_word_embeddings: bool
     embedding_scale: float = 1.0  # the stream starts as embedding[token] * embedding_scale
     logit_scale: float = 1.0  # logits = (head . normed stream) * logit_scale
+    # None: one residual stream [T, hidden].  n >= 1: the blocks work on n streams a token, [T, n, hidden], which all
+    # start as the embedding output and are summed before the final norm (every block must be of such a kind).
+    streams: Optional[int] = None
 
     def validate(self) -> None:
         if not self.layers:

@@ -90,7 +90,8 @@ constexpr int KS = 4;
 constexpr int COLS = 32;
 constexpr int STAGES = 4;
 
-template <int DK, bool VEC>
+// FIXED: the decay is one constant per head (``decay`` holds ``heads`` numbers; a retention), not a row per token.
+template <int DK, bool VEC, bool FIXED>
 __global__ void __launch_bounds__(KS * COLS)
 gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ decay,
                 const int* __restrict__ req_indptr, const int* __restrict__ slots, float* __restrict__ state,
@@ -123,7 +124,7 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
     const int count = last - base < CHUNK ? last - base : CHUNK;
     float* dst = stage + (size_t)buf * CHUNK * row;
     if (VEC) {
-      const int qd = dim >> 2, qv = cols_here >> 2, per_token = 3 * qd + qv;
+      const int qd = dim >> 2, qv = cols_here >> 2, per_token = (FIXED ? 2 : 3) * qd + qv;
       for (int e = tid; e < count * per_token; e += NT) {
         const int tt = e / per_token, rest = e - tt * per_token;
         const int t = base + tt;
@@ -133,19 +134,19 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
           const int what = rest / qd, q4 = rest - what * qd;
           src = proj + (size_t)t * proj_stride + what * hd + h * dim + 4 * q4;
           to = dst + tt * row + what * DK + 4 * q4;
-        } else if (rest < 3 * qd) {
+        } else if (!FIXED && rest < 3 * qd) {
           const int q4 = rest - 2 * qd;
           src = decay + (size_t)t * hd + h * dim + 4 * q4;
           to = dst + tt * row + 2 * DK + 4 * q4;
         } else {
-          const int q4 = rest - 3 * qd;
+          const int q4 = rest - (FIXED ? 2 : 3) * qd;
           src = proj + (size_t)t * proj_stride + 2 * hd + h * vdim + col0 + 4 * q4;
           to = dst + tt * row + 3 * DK + 4 * q4;
         }
         copy16(to, src);
       }
     } else {
-      const int per_token = 3 * dim + cols_here;
+      const int per_token = (FIXED ? 2 : 3) * dim + cols_here;
       for (int e = tid; e < count * per_token; e += NT) {
         const int tt = e / per_token, rest = e - tt * per_token;
         const int t = base + tt;
@@ -155,12 +156,12 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
           const int what = rest / dim, i = rest - what * dim;
           src = proj + (size_t)t * proj_stride + what * hd + h * dim + i;
           to = dst + tt * row + what * DK + i;
-        } else if (rest < 3 * dim) {
+        } else if (!FIXED && rest < 3 * dim) {
           const int i = rest - 2 * dim;
           src = decay + (size_t)t * hd + h * dim + i;
           to = dst + tt * row + 2 * DK + i;
         } else {
-          const int i = rest - 3 * dim;
+          const int i = rest - (FIXED ? 2 : 3) * dim;
           src = proj + (size_t)t * proj_stride + 2 * hd + h * vdim + col0 + i;
           to = dst + tt * row + 3 * DK + i;
         }
@@ -183,6 +184,7 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
     S[n] = (on && i < dim) ? mine[(size_t)i * vdim + col] : 0.f;
   }
 
+  const float fixed = FIXED ? decay[h] : 0.f;
   int buf = 0;
   for (int base = first; base < last; base += CHUNK, buf = (buf + 1) % STAGES) {
     const int count = last - base < CHUNK ? last - base : CHUNK;
@@ -201,7 +203,8 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
       float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
       for (int n = 0; n < PER / 4; ++n) {
-        const float4 a = a4[n * KS + part], k = k4[n * KS + part], q = q4[n * KS + part];
+        const float4 a = FIXED ? make_float4(fixed, fixed, fixed, fixed) : a4[n * KS + part];
+        const float4 k = k4[n * KS + part], q = q4[n * KS + part];
         S[4 * n] = fmaf(k.x, v, a.x * S[4 * n]);
         S[4 * n + 1] = fmaf(k.y, v, a.y * S[4 * n + 1]);
         S[4 * n + 2] = fmaf(k.z, v, a.z * S[4 * n + 2]);
@@ -250,8 +253,27 @@ gla_finish_kernel(const float* __restrict__ o, const float* __restrict__ proj, i
   const float* gate = proj + (size_t)t * proj_stride + gate_offset + h * vdim;
   for (int i = lane; i < vdim; i += 32) {
     const float g = gate[i];
-    out[(size_t)t * hv + h * vdim + i] = from_float<T>(row[i] * inv * weight[i] * (g / (1.f + expf(-g))));
+    out[(size_t)t * hv + h * vdim + i] = from_float<T>(row[i] * inv * (weight ? weight[i] : 1.f) * (g / (1.f + expf(-g))));
   }
+}
+
+// Split-half rotation of the first ``dims`` entries of ``heads`` consecutive heads of ``dim`` entries in float32
+// rows, in place: entry i (< dims / 2) pairs with i + dims / 2, angle = float(position) * inv_freq[i].
+__global__ void rotate_heads_kernel(float* __restrict__ rows, int stride, const int* __restrict__ positions,
+                                    const float* __restrict__ inv_freq, int heads, int dim, int half, size_t total) {
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= total) return;
+  const int i = (int)(e % half);
+  const int h = (int)((e / half) % heads);
+  const size_t t = e / ((size_t)half * heads);
+  float s, c;
+  sincosf((float)positions[t] * inv_freq[i], &s, &c);
+  float* head = rows + t * stride + (size_t)h * dim;
+  const float u = head[i], v = head[i + half];
+  head[i] = u * c - v * s;
+  head[i + half] = v * c + u * s;
 }
 
 }  // namespace
@@ -274,23 +296,26 @@ int tl_gla_decay(const float* proj, int proj_stride, int low_offset, const float
 }
 
 // state: float32 [max_slots, heads, dim, vdim]; out: float32 [tokens, heads * vdim].
+// fixed_decay: ``decay`` holds one constant per head instead of [tokens, heads * dim] rows.
 int tl_gla_scan(const float* proj, int proj_stride, const float* decay, const int* req_indptr, const int* slots,
                 float* state, float* out, int requests, int heads, int dim, int vdim, int max_slots, float qscale,
-                cudaStream_t stream) {
+                int fixed_decay, cudaStream_t stream) {
   if (requests <= 0) return 0;
   if (dim <= 0 || dim > 256 || vdim <= 0 || vdim > 256 || heads > 65535) return TL_ERR_UNSUPPORTED;
   dim3 grid(requests, heads, (vdim + COLS - 1) / COLS);
   const int threads = KS * COLS;
   const bool vec = dim % 4 == 0 && vdim % 4 == 0 && proj_stride % 4 == 0 && (heads * dim) % 4 == 0 &&
-                   (reinterpret_cast<uintptr_t>(proj) & 15) == 0 && (reinterpret_cast<uintptr_t>(decay) & 15) == 0;
-#define TL_SCAN(DK)                                                                                                  \
-  {                                                                                                                  \
-    if (vec)                                                                                                         \
-      tl::launch_kernel(gla_scan_kernel<DK, true>, grid, threads, 0, stream, proj, proj_stride, decay, req_indptr,   \
-                        slots, state, out, heads, dim, vdim, max_slots, qscale);                                     \
-    else                                                                                                             \
-      tl::launch_kernel(gla_scan_kernel<DK, false>, grid, threads, 0, stream, proj, proj_stride, decay,              \
-                        req_indptr, slots, state, out, heads, dim, vdim, max_slots, qscale);                         \
+                   (reinterpret_cast<uintptr_t>(proj) & 15) == 0 &&
+                   (fixed_decay || (reinterpret_cast<uintptr_t>(decay) & 15) == 0);
+#define TL_SCAN_ONE(DK, VEC, FIXED)                                                                                 \
+  tl::launch_kernel(gla_scan_kernel<DK, VEC, FIXED>, grid, threads, 0, stream, proj, proj_stride, decay, req_indptr, \
+                    slots, state, out, heads, dim, vdim, max_slots, qscale)
+#define TL_SCAN(DK)                                                  \
+  {                                                                  \
+    if (vec && fixed_decay) TL_SCAN_ONE(DK, true, true);             \
+    else if (vec) TL_SCAN_ONE(DK, true, false);                      \
+    else if (fixed_decay) TL_SCAN_ONE(DK, false, true);              \
+    else TL_SCAN_ONE(DK, false, false);                              \
   }
   if (dim <= 16) TL_SCAN(16)
   else if (dim <= 32) TL_SCAN(32)
@@ -298,6 +323,17 @@ int tl_gla_scan(const float* proj, int proj_stride, const float* decay, const in
   else if (dim <= 128) TL_SCAN(128)
   else TL_SCAN(256)
 #undef TL_SCAN
+#undef TL_SCAN_ONE
+  return TL_LAUNCH_CHECK();
+}
+
+int tl_rotate_heads_f32(float* rows, int stride, const int* positions, const float* inv_freq, int tokens, int heads,
+                        int dim, int dims, cudaStream_t stream) {
+  if (tokens <= 0 || dims <= 0) return 0;
+  if (dims % 2 || dims > dim || heads <= 0) return TL_ERR_UNSUPPORTED;
+  const size_t total = (size_t)tokens * heads * (dims / 2);
+  tl::launch_kernel(rotate_heads_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, rows, stride, positions,
+                    inv_freq, heads, dim, dims / 2, total);
   return TL_LAUNCH_CHECK();
 }
 

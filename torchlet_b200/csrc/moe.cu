@@ -47,8 +47,11 @@ __device__ __forceinline__ float router_logit(const Row* __restrict__ row, const
 
 // One warp: from a token's router logits (``score``, shared memory, overwritten) to its ``top`` experts and
 // their weights.
+// ``groups`` > 1 with ``keep`` < groups: the experts form ``groups`` equal groups of neighbours, a group is scored by
+// its largest member, and only experts of the ``keep`` best groups (the lower index wins a tie) can be chosen.
 __device__ __forceinline__ void choose_experts(float* score, int experts, int top, int softmax_scores, int renormalize,
-                                               int lane, int* __restrict__ choice, float* __restrict__ weight) {
+                                               int lane, int* __restrict__ choice, float* __restrict__ weight,
+                                               int groups, int keep, float renorm_eps) {
   if (softmax_scores) {
     float m = -INFINITY;
     for (int e = lane; e < experts; e += 32) m = fmaxf(m, score[e]);
@@ -61,6 +64,32 @@ __device__ __forceinline__ void choose_experts(float* score, int experts, int to
     for (int e = lane; e < experts; e += 32) score[e] = 1.f / (1.f + expf(-score[e]));
   }
   __syncwarp();
+  if (groups > 1 && keep < groups) {
+    const int per = experts / groups;
+    // lane g (and g + 32, ...) holds group g's score; ``kept`` groups are marked by a bit per group and lane
+    unsigned long long mine = 0ull;  // bit i: the group lane + 32 i is kept
+    for (int round = 0; round < keep; ++round) {
+      float best = -INFINITY;
+      int at = groups;
+      for (int g = lane, i = 0; g < groups; g += 32, ++i) {
+        if (mine >> i & 1ull) continue;
+        float top_of = -INFINITY;
+        for (int e = g * per; e < (g + 1) * per; ++e) top_of = fmaxf(top_of, score[e]);
+        if (top_of > best) { best = top_of; at = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, best, o);
+        const int other_at = __shfl_xor_sync(0xffffffffu, at, o);
+        if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
+      }
+      if (at < groups && (at & 31) == lane) mine |= 1ull << (at >> 5);
+    }
+    for (int g = lane, i = 0; g < groups; g += 32, ++i)
+      if (!(mine >> i & 1ull))
+        for (int e = g * per; e < (g + 1) * per; ++e) score[e] = -INFINITY;
+    __syncwarp();
+  }
   float total = 0.f;
   for (int j = 0; j < top; ++j) {
     float best = -INFINITY;
@@ -85,7 +114,7 @@ __device__ __forceinline__ void choose_experts(float* score, int experts, int to
     __syncwarp();
   }
   if (renormalize)
-    for (int j = lane; j < top; j += 32) weight[j] /= total;
+    for (int j = lane; j < top; j += 32) weight[j] /= total + renorm_eps;
 }
 
 // One block per token.  The token's row is staged in shared memory as floats; warp w takes the
@@ -94,7 +123,7 @@ template <typename T>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ router, int* __restrict__ choice,
                  float* __restrict__ weight, int tokens, int hidden, int experts, int top, int softmax_scores,
-                 int renormalize) {
+                 int renormalize, int groups, int keep, float renorm_eps) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
   extern __shared__ float xrow[];  // hidden floats
@@ -111,7 +140,7 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ rou
   __syncthreads();
   if (warp != 0) return;
   choose_experts(all_scores, experts, top, softmax_scores, renormalize, lane, choice + (size_t)t * top,
-                 weight + (size_t)t * top);
+                 weight + (size_t)t * top, groups, keep, renorm_eps);
 }
 
 // plan[0] = tiles in use; plan[1 ..] = expert of every tile (-1: none).
@@ -235,9 +264,13 @@ moe_gemm_simt_kernel(const T* __restrict__ x, const T* __restrict__ w, OutT* __r
       if (n >= N) continue;
       float v = acc[i][j];
       if constexpr (GLU) {
-        const float g = fminf(v, limit);
-        const float u = fminf(fmaxf(acc_up[i][j], -limit), limit);
-        v = g / (1.f + expf(-alpha * g)) * (u + 1.f);
+        if (limit > 0.f) {
+          const float g = fminf(v, limit);
+          const float u = fminf(fmaxf(acc_up[i][j], -limit), limit);
+          v = g / (1.f + expf(-alpha * g)) * (u + 1.f);
+        } else {  // no limit: silu(gate) * up
+          v = v / (1.f + expf(-v)) * acc_up[i][j];
+        }
       }
       out[(size_t)m * N + n] = from_float<OutT>(v);
     }
@@ -291,18 +324,22 @@ int tl_moe_tile_rows() { return BM; }
 
 // choice int32 [tokens, top], weight float32 [tokens, top]; router float32 [experts, hidden].
 int tl_moe_route(const void* x, int ldx, int dtype, const float* router, int* choice, float* weight, int tokens,
-                 int hidden, int experts, int top, int softmax_scores, int renormalize, cudaStream_t stream) {
+                 int hidden, int experts, int top, int softmax_scores, int renormalize, int groups, int keep,
+                 float renorm_eps, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (experts <= 0 || experts > MAX_EXPERTS || top <= 0 || top > experts) return TL_ERR_UNSUPPORTED;
+  if (groups < 1 || keep < 1 || keep > groups || experts % groups || top > keep * (experts / groups) || groups > 2048)
+    return TL_ERR_UNSUPPORTED;
   const unsigned blocks = tokens;
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 48 * 1024) return TL_ERR_UNSUPPORTED;
   if (dtype == TL_DTYPE_F32)
     tl::launch_kernel(moe_route_kernel<float>, blocks, ROUTE_WARPS * 32, smem, stream, (const float*)x, ldx, router, choice,
-                      weight, tokens, hidden, experts, top, softmax_scores, renormalize);
+                      weight, tokens, hidden, experts, top, softmax_scores, renormalize, groups, keep, renorm_eps);
   else
     tl::launch_kernel(moe_route_kernel<__nv_bfloat16>, blocks, ROUTE_WARPS * 32, smem, stream, (const __nv_bfloat16*)x,
-                      ldx, router, choice, weight, tokens, hidden, experts, top, softmax_scores, renormalize);
+                      ldx, router, choice, weight, tokens, hidden, experts, top, softmax_scores, renormalize, groups, keep,
+                      renorm_eps);
   return TL_LAUNCH_CHECK();
 }
 

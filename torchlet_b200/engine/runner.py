@@ -216,7 +216,7 @@ class ModelRunner:
     def admit(self, request_id: Hashable) -> int:
         slot = self.cache.admit(request_id)
         self._synced.pop(slot, None)
-        if self.storage.states:
+        if self.storage.states or self.storage.block_states:
             self.storage.clear_slot(slot)
         return slot
 

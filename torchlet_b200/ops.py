@@ -138,7 +138,8 @@ _SIGNATURES = {
     "gla": {
         "tl_gla_decay": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
         "tl_gla_scan": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                        c_int, c_float, c_void_p],
+                        c_int, c_float, c_int, c_void_p],
+        "tl_rotate_heads_f32": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "tl_gla_finish": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
                           c_void_p],
         "tl_gla_debug_error": [c_void_p],
@@ -152,12 +153,31 @@ _SIGNATURES = {
     "moe": {
         "tl_moe_tile_rows": [],
         "tl_moe_route": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                         c_void_p],
+                         c_int, c_int, c_float, c_void_p],
         "tl_moe_plan": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "tl_moe_scatter": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "tl_moe_gemm_simt": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float,
                              c_float, c_void_p],
         "tl_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    },
+    "hyper": {
+        "tl_hyper_fanout": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "tl_hyper_collapse": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "tl_hyper_read_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                               c_float, c_int, c_void_p],
+        "tl_hyper_conv": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                          c_int, c_void_p],
+        "tl_hyper_conv_state": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "tl_hyper_write": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "tl_hyper_debug_error": [c_void_p],
+    },
+    "pooled_attention": {
+        "tl_pooled_store": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "tl_pooled_attention": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                c_float, c_int, c_void_p],
+        "tl_pooled_attention_debug_error": [c_void_p],
     },
     "sampling": {
         "tl_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -458,27 +478,42 @@ def gla_decay(proj, low_offset: int, w2t, bias, decay, rank: int, tau: float) ->
 
 
 def gla_scan(proj, decay, req_indptr, slots, state, out, requests: int, heads: int, dim: int, vdim: int,
-             qscale: float) -> None:
+             qscale: float, fixed_decay: bool = False) -> None:
     """Walks each request's tokens of the step through its slot's state [H, D, V] (float32):
     S = diag(decay) S + k v^T, out = S^T q * qscale; ``proj`` rows are [q (H D) | k (H D) | v (H V) | ...].
+    ``decay`` is float32 [tokens, H D], or with ``fixed_decay`` one constant per head, [H] (a retention).
     A request whose slot is negative is padding."""
     _need_cuda(proj, decay, req_indptr, slots, state, out)
     assert proj.dtype == decay.dtype == state.dtype == out.dtype == torch.float32
+    assert decay.numel() == (heads if fixed_decay else proj.shape[0] * heads * dim)
     assert state.is_contiguous() and out.is_contiguous() and decay.is_contiguous() and proj.stride(1) == 1
     assert state.shape[1:] == (heads, dim, vdim) and req_indptr.dtype == slots.dtype == torch.int32
     code = _fn("gla", "tl_gla_scan")(proj.data_ptr(), proj.stride(0), decay.data_ptr(), req_indptr.data_ptr(),
                                      slots.data_ptr(), state.data_ptr(), out.data_ptr(), requests, heads, dim, vdim,
-                                     state.shape[0], float(qscale), _stream())
+                                     state.shape[0], float(qscale), 1 if fixed_decay else 0, _stream())
     _check(code, "gla_scan")
 
 
+def rotate_heads_f32(rows, positions, inv_freq, heads: int, dim: int, dims: int) -> None:
+    """Split-half rotation, in place, of the first ``dims`` entries of the first ``heads`` heads of ``dim`` entries
+    of every float32 row: entry i pairs with i + dims / 2, angle = float(position) * inv_freq[i]."""
+    _need_cuda(rows, positions, inv_freq)
+    assert rows.dtype == inv_freq.dtype == torch.float32 and rows.stride(1) == 1 and rows.shape[1] >= heads * dim
+    assert positions.dtype == torch.int32 and inv_freq.numel() == dims // 2
+    code = _fn("gla", "tl_rotate_heads_f32")(rows.data_ptr(), rows.stride(0), positions.data_ptr(), inv_freq.data_ptr(),
+                                             rows.shape[0], heads, dim, dims, _stream())
+    _check(code, "rotate_heads_f32")
+
+
 def gla_finish(o, proj, gate_offset: int, weight, out, heads: int, vdim: int, eps: float) -> None:
-    """out = o / rms(o per head) * weight * silu(g), g = proj[:, gate_offset:]; ``weight`` covers one head."""
+    """out = o / rms(o per head) * weight * silu(g), g = proj[:, gate_offset:]; ``weight`` covers one head
+    (None: no weight)."""
     _need_cuda(o, proj, weight, out)
     tokens = o.shape[0]
-    assert o.dtype == weight.dtype == proj.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous()
-    assert out.shape == o.shape == (tokens, heads * vdim) and weight.numel() == vdim
-    code = _fn("gla", "tl_gla_finish")(o.data_ptr(), proj.data_ptr(), proj.stride(0), gate_offset, weight.data_ptr(),
+    assert o.dtype == proj.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous()
+    assert out.shape == o.shape == (tokens, heads * vdim)
+    assert weight is None or (weight.dtype == torch.float32 and weight.numel() == vdim)
+    code = _fn("gla", "tl_gla_finish")(o.data_ptr(), proj.data_ptr(), proj.stride(0), gate_offset, _ptr(weight),
                                        out.data_ptr(), dtype_code(out.dtype), tokens, heads, vdim, float(eps), _stream())
     _check(code, "gla_finish")
 
@@ -503,15 +538,119 @@ def normed_qk_store(proj, wq, wk, inv_freq, magnitude: float, eps: float, positi
     _check(code, "normed_qk_store")
 
 
+# ------------------------------------------- several residual streams, input convolution, layer norm
+def hyper_fanout(acc, z) -> None:
+    """z[t, s] = acc[t] for every stream s;  acc float32 [T, width], z float32 [T, n, width]."""
+    _need_cuda(acc, z)
+    tokens, n, width = z.shape
+    assert acc.dtype == z.dtype == torch.float32 and acc.is_contiguous() and z.is_contiguous() and acc.shape == (tokens, width)
+    _check(_fn("hyper", "tl_hyper_fanout")(acc.data_ptr(), z.data_ptr(), tokens, n, width, _stream()), "hyper_fanout")
+
+
+def hyper_collapse(z, acc) -> None:
+    """acc[t] = sum_s z[t, s] (ascending s)."""
+    _need_cuda(acc, z)
+    tokens, n, width = z.shape
+    assert acc.dtype == z.dtype == torch.float32 and acc.is_contiguous() and z.is_contiguous() and acc.shape == (tokens, width)
+    _check(_fn("hyper", "tl_hyper_collapse")(z.data_ptr(), acc.data_ptr(), tokens, n, width, _stream()), "hyper_collapse")
+
+
+def hyper_read_norm(z, a, weight, bias, eps: float, out, centre: bool = True, rows=None) -> None:
+    """out[r] = norm(sum_s a[s] z[row, s]) * weight (+ bias): a layer norm (``centre``) or an RMS norm of the streams'
+    weighted sum.  z float32 [T, n, width], or [T, width] with ``a`` None; ``rows`` (int32) gathers."""
+    _need_cuda(z, a, weight, bias, out, rows)
+    n = z.shape[1] if z.dim() == 3 else 1
+    width = z.shape[-1]
+    count = out.shape[0]
+    assert z.dtype == weight.dtype == torch.float32 and z.is_contiguous() and out.is_contiguous() and out.shape[1] == width
+    assert (a is None and n == 1) or (a is not None and a.dtype == torch.float32 and a.numel() == n)
+    assert rows is not None or count == z.shape[0]
+    code = _fn("hyper", "tl_hyper_read_norm")(z.data_ptr(), _ptr(a), weight.data_ptr(), _ptr(bias), _ptr(rows), out.data_ptr(),
+                                              dtype_code(out.dtype), count, n, width, float(eps), 1 if centre else 0, _stream())
+    _check(code, "hyper_read_norm")
+
+
+def hyper_conv(h, w, state, token_req, req_indptr, slots, out) -> None:
+    """out[t] = h[t] + sum_j w[:, j] h[t - taps + 1 + j] along each request's tokens; the rows before a request's first
+    token of the step come from ``state`` [slots, taps - 1, width] (float32)."""
+    _need_cuda(h, w, state, token_req, req_indptr, slots, out)
+    tokens, width = h.shape
+    taps = w.shape[1]
+    assert h.dtype == w.dtype == state.dtype == torch.float32 and h.is_contiguous() and w.is_contiguous()
+    assert state.is_contiguous() and state.shape[1:] == (taps - 1, width) and out.is_contiguous() and out.shape == h.shape
+    code = _fn("hyper", "tl_hyper_conv")(h.data_ptr(), w.data_ptr(), state.data_ptr(), token_req.data_ptr(),
+                                         req_indptr.data_ptr(), slots.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
+                                         tokens, width, taps, state.shape[0], _stream())
+    _check(code, "hyper_conv")
+
+
+def hyper_conv_state(h, state, req_indptr, slots, requests: int) -> None:
+    """After ``hyper_conv``: every request's slot keeps the last taps - 1 rows of ``h`` it has seen."""
+    _need_cuda(h, state, req_indptr, slots)
+    width = h.shape[1]
+    taps = state.shape[1] + 1
+    assert h.dtype == state.dtype == torch.float32 and h.is_contiguous() and state.is_contiguous() and state.shape[2] == width
+    code = _fn("hyper", "tl_hyper_conv_state")(h.data_ptr(), state.data_ptr(), req_indptr.data_ptr(), slots.data_ptr(),
+                                               requests, width, taps, state.shape[0], _stream())
+    _check(code, "hyper_conv_state")
+
+
+def hyper_write(z, y, mix, b) -> None:
+    """z[t, to] <- sum_s mix[s, to] z[t, s] + b[to] y[t], all streams from the old ones; y is left zeroed."""
+    _need_cuda(z, y, mix, b)
+    tokens, n, width = z.shape
+    assert z.dtype == y.dtype == mix.dtype == b.dtype == torch.float32 and z.is_contiguous() and y.is_contiguous()
+    assert y.shape == (tokens, width) and mix.is_contiguous() and mix.shape == (n, n) and b.numel() == n
+    _check(_fn("hyper", "tl_hyper_write")(z.data_ptr(), y.data_ptr(), mix.data_ptr(), b.data_ptr(), tokens, n, width,
+                                          _stream()), "hyper_write")
+
+
+# ------------------------------ attention over a window of tokens and pooled blocks of older ones
+def pooled_store(proj, k_offset: int, v_offset: int, pages, block_table, token_req, positions, req_indptr, slots, pooled,
+                 nkv: int, d: int, dv: int, page_size: int, pool: int) -> None:
+    """The step's keys and values (``proj[:, k_offset:]``: nkv x d, ``proj[:, v_offset:]``: nkv x dv) into the
+    pages' rows [key | value]; a token that completes a block of ``pool`` tokens also writes the block's mean row
+    into ``pooled`` [slots, blocks, nkv, d + dv] (float32) of its request's slot (csrc/pooled_attention.cu)."""
+    _need_cuda(proj, pages, block_table, token_req, positions, req_indptr, slots, pooled)
+    assert pages.dtype == proj.dtype and proj.stride(1) == 1 and pages.is_contiguous() and pooled.is_contiguous()
+    assert pooled.dtype == torch.float32 and pooled.shape[2:] == (nkv, d + dv)
+    assert pages.shape[1:] == (1, nkv, page_size, d + dv)
+    code = _fn("pooled_attention", "tl_pooled_store")(
+        proj.data_ptr(), proj.stride(0), k_offset, v_offset, pages.data_ptr(), dtype_code(proj.dtype),
+        block_table.data_ptr(), block_table.shape[1], token_req.data_ptr(), positions.data_ptr(), req_indptr.data_ptr(),
+        slots.data_ptr(), pooled.data_ptr(), pooled.shape[1], pooled.shape[0], proj.shape[0], nkv, d, dv, page_size, pool,
+        pages.shape[0], _stream())
+    _check(code, "pooled_store")
+
+
+def pooled_attention(q, pages, block_table, token_req, positions, slots, pooled, out, nh: int, nkv: int, d: int, dv: int,
+                     page_size: int, size: int, pool: int, scale: float) -> None:
+    """One softmax over the last ``size`` tokens and the pooled rows of the whole blocks before them; one warp a
+    (token, head), float32 inside.  q: rows whose first nh x d entries are the queries."""
+    _need_cuda(q, pages, block_table, token_req, positions, slots, pooled, out)
+    tokens = q.shape[0]
+    assert pages.dtype == q.dtype == out.dtype and q.stride(1) == 1 and out.stride(1) == 1 and pages.is_contiguous()
+    assert out.shape == (tokens, nh * dv) and pooled.dtype == torch.float32 and pooled.is_contiguous()
+    code = _fn("pooled_attention", "tl_pooled_attention")(
+        q.data_ptr(), q.stride(0), pages.data_ptr(), dtype_code(q.dtype), block_table.data_ptr(), block_table.shape[1],
+        token_req.data_ptr(), positions.data_ptr(), slots.data_ptr(), pooled.data_ptr(), pooled.shape[1], pooled.shape[0],
+        out.data_ptr(), out.stride(0), tokens, nh, nkv, d, dv, page_size, size, pool, float(scale), pages.shape[0],
+        _stream())
+    _check(code, "pooled_attention")
+
+
 # ------------------------------------------------------- routed feed-forward
 def moe_tile_rows() -> int:
     """Rows of a tile of the grouped CUDA-core products (every expert's rows are padded to whole tiles)."""
     return _fn("moe", "tl_moe_tile_rows")()
 
 
-def moe_route(x, router, choice, weight, softmax_scores: bool = False, renormalize: bool = False) -> None:
+def moe_route(x, router, choice, weight, softmax_scores: bool = False, renormalize: bool = False, groups: int = 1,
+              keep: int = 1, renorm_eps: float = 0.0) -> None:
     """choice[t, j], weight[t, j]: the ``top`` experts of every token by score (sigmoid or softmax of the
-    float32 router logits) and their scores (csrc/moe.cu)."""
+    float32 router logits) and their scores (csrc/moe.cu), divided by their sum + ``renorm_eps`` if
+    ``renormalize``.  ``groups`` > 1: the experts form that many equal groups of neighbours and only experts of the
+    ``keep`` groups with the largest best score can be chosen."""
     _need_cuda(x, router, choice, weight)
     tokens, hidden = x.shape
     experts, top = router.shape[0], choice.shape[1]
@@ -519,7 +658,7 @@ def moe_route(x, router, choice, weight, softmax_scores: bool = False, renormali
     assert choice.dtype == torch.int32 and weight.dtype == torch.float32 and choice.is_contiguous() and weight.is_contiguous()
     code = _fn("moe", "tl_moe_route")(x.data_ptr(), x.stride(0), dtype_code(x.dtype), router.data_ptr(), choice.data_ptr(),
                                       weight.data_ptr(), tokens, hidden, experts, top, 1 if softmax_scores else 0,
-                                      1 if renormalize else 0, _stream())
+                                      1 if renormalize else 0, int(groups), int(keep), float(renorm_eps), _stream())
     _check(code, "moe_route")
 
 
@@ -986,7 +1125,8 @@ def debug_errors() -> list:
     in the ordinary build (``TORCHLET_B200_DEBUG`` unset), whose kernels carry no checks."""
     found = []
     for library in ("elementwise", "attention_generic", "attention_mma", "decode_fused", "slots", "stream_ops",
-                    "delta_rule", "latent_attention", "latent_attention_mma", "gla", "gated_attention"):
+                    "delta_rule", "latent_attention", "latent_attention_mma", "gla", "gated_attention", "hyper",
+                    "pooled_attention"):
         if any(name in _functions for name in _SIGNATURES[library]):
             value = ctypes.c_int(0)
             code = _fn(library, f"tl_{library}_debug_error")(ctypes.byref(value))

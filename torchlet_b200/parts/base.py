@@ -28,7 +28,8 @@ class TensorSpec:
 
     name: str
     shape: tuple
-    init: str = "normal"  # "normal": N(0, std); "ones": 1 + N(0, norm_std); "zeros": N(0, norm_std)
+    # "normal": N(0, std); "ones": 1 + N(0, norm_std); "zeros": N(0, norm_std); "eye": identity + N(0, norm_std)
+    init: str = "normal"
     optional: bool = False
 
 
@@ -50,11 +51,19 @@ class KVSpec:
 
 @dataclass(frozen=True)
 class StateSpec:
-    """Fixed-size state a mixer keeps per live request (one row per slot),
-    zeroed when a request is admitted."""
+    """Fixed-size state a part keeps per live request (one row per slot), zeroed when a request is
+    admitted.  ``per_tokens`` = P: the state is one ``shape`` entry for every P tokens of the longest
+    sequence the engine admits, ``[ceil(max_seq_len / P), *shape]`` a slot (a summary row per block of
+    tokens, for instance)."""
 
     shape: tuple
     dtype: str = "float32"
+    per_tokens: Optional[int] = None
+
+    def slot_shape(self, max_seq_len: int) -> tuple:
+        if self.per_tokens is None:
+            return tuple(self.shape)
+        return (-(-max_seq_len // self.per_tokens), *self.shape)
 
 
 class Part:
@@ -118,7 +127,9 @@ class Mixer(Part):
     def kv_spec(self) -> Optional[KVSpec]:
         return None
 
-    def state_spec(self) -> Optional[StateSpec]:
+    def state_spec(self):
+        """None, one ``StateSpec``, or a dict name -> ``StateSpec`` for a mixer that keeps several
+        states (``cache.state`` is then a dict of tensors under the same names)."""
         return None
 
     def forward(self, ctx, x, acc, cache) -> None:
@@ -165,6 +176,19 @@ class Block:
         self.norms = dict(norms)
         self.params = dict(params or {})
         self.token_input = token_input
+
+    @classmethod
+    def expected_tensors(cls, layer) -> list:
+        """Tensors of the arrangement itself (not of its parts), by full name; ``layer``: the ``LayerSpec``."""
+        return []
+
+    def load(self, tensors: dict, layer, device, dtype) -> None:
+        """Take the arrangement's own tensors."""
+
+    def state_spec(self):
+        """State the arrangement itself keeps per live request (None, a ``StateSpec`` or a dict of them);
+        ``cache.block_state`` holds it."""
+        return None
 
     def forward(self, ctx, acc, cache) -> None:
         raise NotImplementedError

@@ -22,7 +22,8 @@ class ExecutionCacheNeed:
     entry: int
     owner: int  # the entry whose cache is used (itself unless cache_from is set)
     kv: Optional[KVSpec]
-    state: Optional[StateSpec]
+    state: object  # the mixer's: None, a StateSpec, or a dict name -> StateSpec
+    block_state: object = None  # the block arrangement's own, in the same forms
 
 
 def _layer_parts(layer) -> list:
@@ -43,6 +44,7 @@ def expected_tensors(spec: ModelSpec) -> list[TensorSpec]:
     for layer in spec.layers:
         for registry, part, prefix, _ in _layer_parts(layer):
             out += registry.get(part.kind).expected_tensors(part, prefix)
+        out += BLOCKS.get(layer.block).expected_tensors(layer)
     out += NORMS.get(spec.final_norm.kind).expected_tensors(spec.final_norm, spec.final_norm_prefix)
     out.append(TensorSpec(spec.lm_head_name, (spec.vocab_size, spec.hidden_size), optional=spec.tie_word_embeddings))
     unique, seen = [], set()
@@ -89,7 +91,8 @@ class LayeredModel:
                 mine = mixer.kv_spec()
                 if theirs is None or mine is None or (theirs.num_kv_heads, theirs.head_dim, theirs.planes) != (mine.num_kv_heads, mine.head_dim, mine.planes):
                     raise ValueError(f"schedule entry {i} cannot read the cache of entry {owner}: shapes differ")
-            needs.append(ExecutionCacheNeed(i, owner, mixer.kv_spec(), mixer.state_spec()))
+            needs.append(ExecutionCacheNeed(i, owner, mixer.kv_spec(), mixer.state_spec(),
+                                            self.blocks[entry.layer].state_spec()))
         return needs
 
     # --------------------------------------------------------------- weights
@@ -103,6 +106,7 @@ class LayeredModel:
                 part = {"mixer": block.mixer, "feed_forward": block.feed_forward,
                         "token_input": getattr(block, "token_input", None)}.get(role) or block.norms[role]
                 part.load(tensors, prefix, device, dtype)
+            block.load(tensors, layer, device, dtype)
         self.final_norm.load(tensors, spec.final_norm_prefix, device, dtype)
         if spec.tie_word_embeddings:
             self.lm_head = Linear.from_device_weight(self.embedding)
@@ -114,9 +118,19 @@ class LayeredModel:
         """Run the step's tokens through the schedule; returns the float32 stream [T, hidden]."""
         acc = ctx.buffer("stream", (ctx.num_tokens, self.spec.hidden_size), torch.float32)
         ops.embed(self.embedding, ctx.tokens, acc, self.spec.embedding_scale)
+        streams = self.spec.streams
+        if streams is None:
+            for i, entry in enumerate(self.spec.schedule):
+                self.blocks[entry.layer].forward(ctx, acc, caches[i])
+            ctx.flush_pending()
+            return acc
+        # several residual streams a token, all equal to the embedding at the start; their sum at the end
+        z = ctx.buffer("streams", (ctx.num_tokens, streams, self.spec.hidden_size), torch.float32)
+        ops.hyper_fanout(acc, z)
         for i, entry in enumerate(self.spec.schedule):
-            self.blocks[entry.layer].forward(ctx, acc, caches[i])
+            self.blocks[entry.layer].forward(ctx, z, caches[i])
         ctx.flush_pending()
+        ops.hyper_collapse(z, acc)
         return acc
 
     def logits(self, ctx, acc: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:

@@ -41,6 +41,7 @@ class RMSNorm(Norm):
         if self.weight_offset:
             self.weight += self.weight_offset
 
+    centre = False  # no mean is taken off (what a block that norms inside its own kernel asks)
     fuses_pending = True  # a product's unfinished sum into the stream is completed in the norm's own kernel
 
     def forward(self, ctx, acc, out=None, rows=None, name="normed"):
@@ -74,3 +75,41 @@ class RMSNorm(Norm):
         else:
             ctx.flush_pending()
         ops.rms_scaled_add(acc, y, self.weight, m, self.eps, clear)
+
+
+@NORMS.register("layer_norm")
+class LayerNorm(Norm):
+    """y = (x - mean) / sqrt(variance + eps) * w + b, the variance being the mean of the squared deviations;
+    float32 inside (csrc/hyper.cu).  Parameters: ``size``, ``eps``, ``weight_name`` (default "weight"; "" when the
+    prefix itself is the tensor's name), ``bias_name`` (default "bias"; None: no bias)."""
+
+    centre = True
+
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        self.size = int(spec.params["size"])
+        self.eps = float(spec.params["eps"])
+        self.weight = self.bias = None
+
+    @classmethod
+    def _names(cls, spec: PartSpec, prefix: str) -> tuple:
+        bias = spec.params.get("bias_name", "bias")
+        return prefix + spec.params.get("weight_name", "weight"), (prefix + bias if bias is not None else None)
+
+    @classmethod
+    def expected_tensors(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
+        weight, bias = cls._names(spec, prefix)
+        size = int(spec.params["size"])
+        return [TensorSpec(weight, (size,), init="ones")] + ([TensorSpec(bias, (size,), init="zeros")] if bias else [])
+
+    def load(self, tensors: dict, prefix: str, device, dtype) -> None:
+        weight, bias = self._names(self.spec, prefix)
+        self.weight = tensors[weight].to(device=device, dtype=torch.float32).contiguous()
+        self.bias = tensors[bias].to(device=device, dtype=torch.float32).contiguous() if bias else None
+
+    def forward(self, ctx, acc, out=None, rows=None, name="normed"):
+        count = acc.shape[0] if rows is None else rows.numel()
+        if out is None:
+            out = ctx.buffer(name, (count, self.size), ctx.dtype)
+        ops.hyper_read_norm(acc, None, self.weight, self.bias, self.eps, out, centre=True, rows=rows)
+        return out

@@ -1,0 +1,67 @@
+"""Several mixers side by side: all read the same input, the result is the weighted sum of theirs,
+sum_i scale_i mixer_i(x).
+
+Parameters: ``branches``: a list of {"mixer": PartSpec, "prefix": tensor prefix below this mixer's, "scale": float}.
+Each branch keeps what its own kind keeps; at most one branch may keep paged history (the execution has one page
+group), any number may keep per-request state (the execution's state is a dict by branch prefix).  A branch whose
+scale is 1 adds straight into the stream; any other adds into a zeroed float32 stream of its own, and the scaled
+sum into the stream is one float32 operation, so no weight is rescaled and nothing is rounded twice.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+
+from .. import ops
+from ..config.spec import PartSpec
+from .base import MIXERS, Mixer, TensorSpec, build_part
+
+
+@MIXERS.register("parallel_mixers")
+class ParallelMixers(Mixer):
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        branches = spec.params["branches"]
+        if not branches:
+            raise ValueError("a parallel mixer needs at least one branch")
+        self.branches = [(str(b["prefix"]), build_part(MIXERS, b["mixer"]), float(b.get("scale", 1.0))) for b in branches]
+        if len({prefix for prefix, _, _ in self.branches}) != len(self.branches):
+            raise ValueError("the branches of a parallel mixer need different prefixes")
+        if sum(1 for _, part, _ in self.branches if part.kv_spec() is not None) > 1:
+            raise ValueError("at most one branch of a parallel mixer may keep paged history")
+        self.graph_safe = all(getattr(part, "graph_safe", False) for _, part, _ in self.branches)
+
+    def kv_spec(self):
+        for _, part, _ in self.branches:
+            if part.kv_spec() is not None:
+                return part.kv_spec()
+        return None
+
+    def state_spec(self):
+        specs = {prefix: part.state_spec() for prefix, part, _ in self.branches if part.state_spec() is not None}
+        return specs or None
+
+    @classmethod
+    def expected_tensors(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
+        out = []
+        for branch in spec.params["branches"]:
+            out += MIXERS.get(branch["mixer"].kind).expected_tensors(branch["mixer"], prefix + branch["prefix"])
+        return out
+
+    def load(self, tensors: dict, prefix: str, device, dtype) -> None:
+        for name, part, _ in self.branches:
+            part.load(tensors, prefix + name, device, dtype)
+
+    def forward(self, ctx, x, acc, cache) -> None:
+        states = cache.state or {}
+        for name, part, scale in self.branches:
+            mine = dataclasses.replace(cache, state=states.get(name))
+            if scale == 1.0:
+                part.forward(ctx, x, acc, mine)
+                continue
+            side = ctx.buffer("parallel_mixers.side", tuple(acc.shape), torch.float32)
+            ops.fill_zero(side)
+            part.forward(ctx, x, side, mine)
+            ctx.flush_pending()
+            ops.scaled_add(acc, side, scale)

@@ -1,11 +1,14 @@
-"""A routed feed-forward (mixture of experts) of clamped gated units.
+"""A routed feed-forward (mixture of experts) of gated units, clamped or plain.
 
 Router: z = W_router x in float32, scores sigmoid(z) (``score`` "sigmoid") or softmax(z) ("softmax");
 every token uses the ``top_k`` experts with the largest scores (the lower index wins a tie); the
 weights are those scores, divided by their sum if ``renormalize``.  Expert e: g = min(W_gate,e h, limit),
 u = clamp(W_up,e h, -limit, limit), y = g sigmoid(alpha g) (u + 1), output W_down,e y, no biases.  The
 weight multiplies the expert's INPUT (``weight_on`` "input": out = sum_j expert_j(w_j x)) or its output
-("output": out = sum_j w_j expert_j(x)).
+("output": out = sum_j w_j expert_j(x)).  ``limit`` None: the expert is the plain gated unit
+W_down,e (silu(W_gate,e h) * W_up,e h).  ``groups`` > 1 with ``keep`` < groups: the experts form ``groups``
+equal groups of neighbours, a group's score is its largest member's, and only experts of the ``keep`` best groups
+can be chosen.  With ``renormalize`` the chosen scores are divided by their sum + ``renorm_eps``.
 
 Routing, the expert-sorted order and the products are planned and run on the device (csrc/moe.cu):
 nothing is read back, so steps of single tokens are captured like any other part's.  In bfloat16 the
@@ -15,7 +18,7 @@ activation in its epilogue over gate and up rows interleaved by 16; in float32, 
 kernel does not take, on CUDA cores in tiles of 64 rows.
 
 Parameters: ``hidden_size``, ``intermediate_size``, ``limit``, ``alpha``, ``num_experts``, ``top_k``,
-``score``, ``renormalize``, ``weight_on``.  Tensors below the prefix: router [E, hidden];
+``score``, ``renormalize``, ``renorm_eps``, ``weight_on``, ``groups``, ``keep``.  Tensors below the prefix: router [E, hidden];
 e<j>.gate, e<j>.up [ff, hidden]; e<j>.down [hidden, ff].
 """
 from __future__ import annotations
@@ -34,13 +37,22 @@ class RoutedClampedGLU(FeedForward):
         p = spec.params
         self.hidden_size = int(p["hidden_size"])
         self.intermediate_size = int(p["intermediate_size"])
-        self.limit = float(p["limit"])
+        self.limit = float(p["limit"]) if p.get("limit") is not None else 0.0  # 0: no clamp, silu(gate) * up
+        if p.get("limit") is not None and not self.limit > 0:
+            raise ValueError("limit must be positive (or None for the plain gated unit)")
         self.alpha = float(p.get("alpha", 1.702))
         self.num_experts = int(p["num_experts"])
         self.top_k = int(p["top_k"])
         self.score = p.get("score", "sigmoid")
         self.renormalize = bool(p.get("renormalize", False))
         self.weight_on = p.get("weight_on", "output")
+        self.renorm_eps = float(p.get("renorm_eps", 0.0))
+        self.groups = int(p.get("groups", 1))
+        self.keep = int(p.get("keep", self.groups))
+        if self.groups < 1 or self.num_experts % self.groups or not 1 <= self.keep <= self.groups:
+            raise ValueError(f"{self.num_experts} experts cannot form {self.groups} equal groups of which {self.keep} are kept")
+        if self.top_k > self.keep * (self.num_experts // self.groups):
+            raise ValueError(f"top_k {self.top_k} exceeds the {self.keep} kept groups' experts")
         if self.score not in ("sigmoid", "softmax"):
             raise ValueError(f"unknown router score {self.score!r} (known: sigmoid, softmax)")
         if self.weight_on not in ("input", "output"):
@@ -108,7 +120,8 @@ class RoutedClampedGLU(FeedForward):
         act = ctx.buffer("moe.act", (most_rows, self.intermediate_size), ctx.dtype)[:rows]
         y = ctx.buffer("moe.y", (most_rows, self.hidden_size), torch.float32)[:rows]
         on_input = self.weight_on == "input"
-        ops.moe_route(x, self.router, choice, weight, self.score == "softmax", self.renormalize)
+        ops.moe_route(x, self.router, choice, weight, self.score == "softmax", self.renormalize, self.groups, self.keep,
+                      self.renorm_eps)
         ops.moe_plan(choice, position, plan, E, tile)
         ops.moe_scatter(x, position, weight, sorted_x, top, weighted=on_input)
         if self.tensor_cores:

@@ -2,7 +2,8 @@
 configuration and a seed, so that everything downstream goes through the loader.
 
 Matrices, embeddings and biases are N(0, std); norm weights are 1 + N(0, norm_std)
-(norm_std 0 gives exact ones), or N(0, norm_std) for norms whose weight is stored around zero.  Tensors are drawn on the CPU in float32 in the order of
+(norm_std 0 gives exact ones), or N(0, norm_std) for norms whose weight is stored around zero; a matrix marked "eye"
+is the identity + N(0, norm_std).  Tensors are drawn on the CPU in float32 in the order of
 the model's expected-tensor list from one ``torch.Generator(seed)``, then cast.
 """
 from __future__ import annotations
@@ -28,8 +29,11 @@ def random_tensors(config, seed: int, std: float = 0.02, norm_std: float = 0.0, 
     for want in expected_tensors(spec):
         if want.optional:  # tied LM head: not stored
             continue
-        if want.init in ("ones", "zeros"):
-            value = torch.full(want.shape, 1.0 if want.init == "ones" else 0.0, dtype=torch.float32, device=device)
+        if want.init in ("ones", "zeros", "eye"):
+            if want.init == "eye":
+                value = torch.eye(want.shape[0], want.shape[1], dtype=torch.float32, device=device)
+            else:
+                value = torch.full(want.shape, 1.0 if want.init == "ones" else 0.0, dtype=torch.float32, device=device)
             if norm_std:
                 value += torch.randn(want.shape, generator=generator, dtype=torch.float32, device=device) * norm_std
         else:
