@@ -178,7 +178,8 @@ def forward(cfg: dict, weights: dict, ids, streams: list | None = None) -> torch
             if sub == "mlp" and layer.get("mlp") is None:
                 continue
             h = layer_norm(stream_read(z, w[f"{p}hc{which}.in"]), w[f"{p}norm{which}"], w[f"{p}norm{which}.b"], eps)
-            h = h + causal_conv(h, w[f"{p}canon{which}"])
+            if cfg.get("canon"):
+                h = h + causal_conv(h, w[f"{p}canon{which}"])
             if sub == "mixer":
                 y = parallel_mixer(h, w, p + "mix.", layer["mixer"], eps)
             elif layer["mlp"]["kind"] == "dense":

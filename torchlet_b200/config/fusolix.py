@@ -68,8 +68,8 @@ class FusolixConfig:
         _positive_int(self.streams, "streams")
         if self.streams > 8:
             raise ValueError("at most 8 streams are supported")
-        if self.canon_taps is not None and not 2 <= self.canon_taps <= 8:
-            raise ValueError(f"canon.taps {self.canon_taps} is not supported (2 to 8)")
+        if self.canon_taps is not None and not 1 <= self.canon_taps <= 8:
+            raise ValueError(f"canon.taps {self.canon_taps} is not supported (1 to 8)")
         if not self.norm_eps > 0:
             raise ValueError("norm.eps must be positive")
         if not self.layers:
@@ -134,8 +134,6 @@ class FusolixConfig:
             streams=int(raw.get("streams", 1)), norm_eps=float((raw.get("norm") or {}).get("eps", 1e-6)),
             embedding_scale=float((raw.get("embedding") or {}).get("scale", 1.0)),
             canon_taps=int(canon["taps"]) if canon.get("taps") else None, eos_token_id=raw.get("eos_token_id"))
-        if values["canon_taps"] == 1:  # one tap is a per-channel factor on the token itself, no history
-            raise ValueError("canon.taps 1 is not supported (2 to 8)")
         if raw.get("max_position_embeddings") is not None:
             values["max_position_embeddings"] = int(raw["max_position_embeddings"])
         return cls(**values)

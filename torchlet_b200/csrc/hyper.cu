@@ -207,7 +207,7 @@ int tl_hyper_conv(const float* h, const float* w, const float* state, const int*
                   cudaStream_t stream) {
   const size_t total = (size_t)tokens * width;
   if (total == 0) return 0;
-  if (taps < 2 || taps > MAX_TAPS) return TL_ERR_UNSUPPORTED;
+  if (taps < 1 || taps > MAX_TAPS || (taps > 1 && state == nullptr)) return TL_ERR_UNSUPPORTED;  // one tap: no history
   const unsigned blocks = (unsigned)((total + 255) / 256);
   if (out_dtype == TL_DTYPE_F32)
     tl::launch_kernel(conv_kernel<float>, blocks, 256, 0, stream, h, w, state, token_req, req_indptr, slots, (float*)out,

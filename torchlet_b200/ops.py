@@ -572,15 +572,17 @@ def hyper_read_norm(z, a, weight, bias, eps: float, out, centre: bool = True, ro
 
 def hyper_conv(h, w, state, token_req, req_indptr, slots, out) -> None:
     """out[t] = h[t] + sum_j w[:, j] h[t - taps + 1 + j] along each request's tokens; the rows before a request's first
-    token of the step come from ``state`` [slots, taps - 1, width] (float32)."""
+    token of the step come from ``state`` [slots, taps - 1, width] (float32; None with one tap, which has no history)."""
     _need_cuda(h, w, state, token_req, req_indptr, slots, out)
     tokens, width = h.shape
     taps = w.shape[1]
-    assert h.dtype == w.dtype == state.dtype == torch.float32 and h.is_contiguous() and w.is_contiguous()
-    assert state.is_contiguous() and state.shape[1:] == (taps - 1, width) and out.is_contiguous() and out.shape == h.shape
-    code = _fn("hyper", "tl_hyper_conv")(h.data_ptr(), w.data_ptr(), state.data_ptr(), token_req.data_ptr(),
+    assert h.dtype == w.dtype == torch.float32 and h.is_contiguous() and w.is_contiguous() and w.shape[0] == width
+    assert out.is_contiguous() and out.shape == h.shape
+    if taps > 1:
+        assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (taps - 1, width)
+    code = _fn("hyper", "tl_hyper_conv")(h.data_ptr(), w.data_ptr(), _ptr(state) if taps > 1 else 0, token_req.data_ptr(),
                                          req_indptr.data_ptr(), slots.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
-                                         tokens, width, taps, state.shape[0], _stream())
+                                         tokens, width, taps, state.shape[0] if taps > 1 else 0, _stream())
     _check(code, "hyper_conv")
 
 

@@ -111,8 +111,8 @@ class HyperConnectedBlock(Block):
             raise ValueError(f"block arrangement {self.kind!r} with a feed-forward needs a norm for the role 'feed_forward_norm'")
         self.streams = int(self.params.get("streams", 1))
         self.taps = int(self.params["taps"]) if self.params.get("taps") else None
-        if self.taps is not None and not 2 <= self.taps <= 8:
-            raise ValueError(f"a convolution of {self.taps} taps is not supported (2 to 8)")
+        if self.taps is not None and not 1 <= self.taps <= 8:
+            raise ValueError(f"a convolution of {self.taps} taps is not supported (1 to 8)")
         if not 1 <= self.streams <= 8:
             raise ValueError(f"{self.streams} streams are not supported (1 to 8)")
         for norm in norms.values():
@@ -156,7 +156,7 @@ class HyperConnectedBlock(Block):
             self.conv[which] = f32(layer.prefix + convolution) if convolution is not None else None
 
     def state_spec(self):
-        if self.taps is None:
+        if self.taps is None or self.taps == 1:  # one tap reads the token itself: nothing to keep
             return None
         from .base import StateSpec
 
@@ -173,9 +173,10 @@ class HyperConnectedBlock(Block):
         x = h
         if conv is not None:
             x = ctx.buffer("hyper.x", (tokens, width), ctx.dtype)
-            state = cache.block_state[which]
+            state = cache.block_state[which] if self.taps > 1 else None
             ops.hyper_conv(h, conv, state, ctx.token_req, ctx.req_indptr, ctx.slots, x)
-            ops.hyper_conv_state(h, state, ctx.req_indptr, ctx.slots, ctx.num_requests)
+            if state is not None:
+                ops.hyper_conv_state(h, state, ctx.req_indptr, ctx.slots, ctx.num_requests)
         side = ctx.buffer("hyper.side", (tokens, width), torch.float32)
         if ctx.plans.get("hyper.side.clean") != side.data_ptr():  # the step's first sub-layer; the write kernel clears it after
             ops.fill_zero(side)
