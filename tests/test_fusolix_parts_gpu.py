@@ -117,11 +117,38 @@ def test_input_convolution_carries_its_history_in_the_slot(taps, width):
 
 
 # ------------------------------------------- attention over a window and pooled blocks
-def _run_pooled(q, k, v, cuts, page_size, size, pool, scale, dtype, poison=True, seed=0):
+class _Step:
+    """What the bfloat16 dispatcher of the attention kernels reads of a step: ONE request that brings ``n`` tokens
+    behind ``before`` cached ones, its pooled rows in slot 1."""
+
+    def __init__(self, before, n, mixer):
+        import numpy as np
+
+        self.mixer, self.plans, self.dtype = mixer, {}, torch.bfloat16
+        self.num_tokens, self.num_requests, self.decode_only, self.max_kv_len = n, 1, n == 1, before + n
+        self.req_indptr_host, self.kv_before_host = np.array([0, n], dtype=np.int32), np.array([before], dtype=np.int32)
+        self.req_indptr, self.kv_before, self.slots = ints([0, n]), ints([before]), ints([1])
+        self.positions = torch.arange(before, before + n, dtype=torch.int32, device=DEV)
+        self.token_req = torch.zeros(n, dtype=torch.int32, device=DEV)
+
+    def upload(self, values):
+        return torch.from_numpy(values).to(DEV)
+
+    def buffer(self, name, shape, dtype):
+        return torch.full(shape, float("nan"), dtype=dtype, device=DEV)
+
+
+def _run_pooled(q, k, v, cuts, page_size, size, pool, scale, dtype, poison=True, seed=0, layout="joined"):
     """q [T, H, d], k [T, G, d], v [T, G, dv] of ONE request through the store and attention kernels in portions
     ``cuts``; pages in shuffled order in a pool full of NaN, the pooled rows in slot 1 of three slots full of NaN;
-    after every step the pages that lie wholly before the window and the open block are filled with NaN again."""
+    after every step the pages that lie wholly before the window and the open block are filled with NaN again.
+    ``layout``: "joined" rows [key | value]; "split": a key plane and a value plane, the same kernel; "tensor": the
+    split planes read by the tensor-core kernels, which join the pooled rows' softmax state."""
+    from types import SimpleNamespace
+
     from torchlet_b200 import ops
+    from torchlet_b200.cache.storage import LayerCache
+    from torchlet_b200.parts import pooled_attention_bf16
 
     td = TORCH[dtype]
     T, H, d = q.shape
@@ -132,7 +159,11 @@ def _run_pooled(q, k, v, cuts, page_size, size, pool, scale, dtype, poison=True,
     g = torch.Generator().manual_seed(70 + seed)
     order = torch.randperm(num_pages, generator=g)[:used]
     table = order.int().view(1, used).to(DEV)
-    pages = torch.full((num_pages, 1, G, page_size, d + dv), float("nan"), dtype=td, device=DEV)
+    if layout == "joined":
+        pages = torch.full((num_pages, 1, G, page_size, d + dv), float("nan"), dtype=td, device=DEV)
+    else:
+        pages = torch.full((num_pages, 2, G, page_size, d), float("nan"), dtype=td, device=DEV)
+    mixer = SimpleNamespace(head_dim=d, v_dim=dv, num_heads=H, num_kv_heads=G, window=size, pool=pool, scale=scale)
     max_blocks = -(-T // pool)
     pooled = torch.full((3, max_blocks, G, d + dv), float("nan"), device=DEV)
     out = torch.full((T, H * dv), float("nan"), dtype=td, device=DEV)
@@ -143,12 +174,20 @@ def _run_pooled(q, k, v, cuts, page_size, size, pool, scale, dtype, poison=True,
         part = proj[at:at + n]
         ops.pooled_store(part, H * d, H * d + G * d, pages, table, req, positions, ints([0, n]), ints([1]), pooled, G, d, dv,
                          page_size, pool)
-        ops.pooled_attention(part, pages, table, req, positions, ints([1]), pooled, out[at:at + n], H, G, d, dv, page_size,
-                             size, pool, scale)
+        if layout == "tensor":
+            # poisoned pages hold NaN; the tensor-core kernels load whole tiles and mask the scores, but 0 x NaN
+            # would spoil P V: as in the engine, stale pages hold finite numbers
+            pages.nan_to_num_(nan=1e4)
+            step = _Step(at, n, mixer)
+            cache = LayerCache(pages, table, page_size, pooled, writable=True)
+            assert pooled_attention_bf16.forward(mixer, step, part, cache, out[at:at + n])
+        else:
+            ops.pooled_attention(part, pages, table, req, positions, ints([1]), pooled, out[at:at + n], H, G, d, dv,
+                                 page_size, size, pool, scale)
         at += n
         if poison:
             for p in range(max(0, at - max(size, pool)) // page_size):
-                pages[int(order[p])] = float("nan")
+                pages[int(order[p])] = float("nan") if layout != "tensor" else 1e4
     assert at == T
     assert torch.isnan(pooled[0]).all() and torch.isnan(pooled[2]).all(), "other requests' slots are not touched"
     return out.float().cpu().view(T, H, dv)
@@ -172,7 +211,8 @@ def _aim(q, k, scale, i, j, score=14.0):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,d,dv,size,pool,page_size", [
     (4, 2, 24, 16, 13, 5, 16), (1, 1, 40, 8, 1, 1, 8), (2, 1, 12, 40, 7, 16, 8), (6, 3, 8, 8, 20, 4, 16),
-    (4, 1, 64, 64, 150, 16, 16), (6, 2, 128, 64, 70, 24, 32), (2, 2, 64, 128, 33, 8, 16), (3, 1, 256, 72, 16, 16, 16)])
+    (4, 1, 64, 64, 150, 16, 16), (6, 2, 128, 64, 70, 24, 32), (2, 2, 64, 128, 33, 8, 16), (3, 1, 256, 72, 16, 16, 16),
+    (8, 2, 128, 128, 40, 8, 64), (3, 3, 64, 64, 129, 3, 24), (2, 1, 24, 24, 10, 7, 8)])
 def test_window_and_pooled_blocks_on_designed_keys(dtype, H, G, d, dv, size, pool, page_size):
     """Queries that point at the key just inside the window, at the key just outside it (seen only if it ends a block,
     and then as its block's mean), at a token of the newest block that is seen and of the next one, which is not yet;
@@ -209,13 +249,21 @@ def test_window_and_pooled_blocks_on_designed_keys(dtype, H, G, d, dv, size, poo
     if dtype == "float32":  # the order of every sum depends on the position alone
         assert torch.equal(whole, decoded) and torch.equal(whole, portions)
     assert probes
+    if d == dv:
+        split = _run_pooled(q, k, v, cuts, page_size, size, pool, scale, dtype, seed=3, layout="split")
+        assert torch.equal(split, portions), "a key plane and a value plane hold the same numbers as joined rows"
+        if dtype == "bfloat16" and d in (64, 128):
+            for name, these in (("a whole prompt", [T]), ("decoded", [T - 40] + [1] * 40), ("portions", cuts)):
+                got = _run_pooled(q, k, v, these, page_size, size, pool, scale, dtype, seed=4, layout="tensor")
+                close(got, want, tol, f"tensor cores: {name}")
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_one_block_far_back_among_hundreds(dtype):
+@pytest.mark.parametrize("dtype,d,layout", [("float32", 16, "joined"), ("bfloat16", 16, "joined"), ("float32", 64, "split"),
+                                             ("bfloat16", 64, "tensor"), ("bfloat16", 128, "tensor")])
+def test_one_block_far_back_among_hundreds(dtype, d, layout):
     """700 tokens in blocks of 4 behind a window of 20: the last queries point at a key of block 3; its value, through
-    the block's mean, is what comes out.  Then the same with the block's row spoilt: the output must change."""
-    T, H, G, d, dv, size, pool = 700, 2, 1, 16, 16, 20, 4
+    the block's mean, is what comes out."""
+    T, H, G, dv, size, pool = 700, 2, 1, d, 20, 4
     td = TORCH[dtype]
     scale = 0.25
     q, k, v = rand(T, H, d, seed=4), rand(T, G, d, seed=5, scale=0.3), rand(T, G, dv, seed=6, scale=0.3)
@@ -229,7 +277,7 @@ def test_one_block_far_back_among_hundreds(dtype):
     want = _plain_pooled(q, k, v, scale, size, pool)
     tol = 2e-5 if dtype == "float32" else 2e-2
     for cuts in ([T], [T - 8] + [1] * 8, [350, 2, 340, 8]):
-        got = _run_pooled(q, k, v, cuts, 16, size, pool, scale, dtype)
+        got = _run_pooled(q, k, v, cuts, 16, size, pool, scale, dtype, layout=layout)
         close(got, want, tol, f"cuts {cuts[:3]}")
         close(got[-1, 0], v[13, 0], 5e-2, "the far block's value")
 

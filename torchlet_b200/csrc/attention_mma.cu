@@ -74,6 +74,11 @@ struct Params {
   int sink;
   const float* gate;
   long long gate_stride;
+  // a PRIOR softmax state of every (token, head), computed elsewhere over keys this kernel does not walk (summary
+  // rows of older tokens, for instance): prior_ml [tokens][nh][2] = (max in log2 units, sum), prior_acc
+  // [tokens][nh][D] the unnormalized weighted values; max = -inf: none.  It joins wherever a row is normalized.
+  const float* prior_ml;
+  const float* prior_acc;
 };
 
 __device__ __forceinline__ float capped_tanh(float x) { return 1.f - 2.f / (__expf(2.f * x) + 1.f); }
@@ -81,6 +86,28 @@ __device__ __forceinline__ float capped_tanh(float x) { return 1.f - 2.f / (__ex
 template <bool EXTRAS> __device__ __forceinline__ float with_sink(const Params& p, float l, float m) {
   if constexpr (!EXTRAS) return l;
   return (p.sink && m != -INFINITY) ? l + exp2f(-m) : l;
+}
+// The factors that bring a row's own state (max m) and its prior (max prior.x) to their common max, which replaces m.
+struct PriorFactors { float own, theirs, sum; };
+template <bool EXTRAS> __device__ __forceinline__ PriorFactors prior_of(const Params& p, int token, int head, float& m) {
+  PriorFactors f{1.f, 0.f, 0.f};
+  if constexpr (EXTRAS) {
+    if (p.prior_ml) {
+      const float2 ml = *reinterpret_cast<const float2*>(p.prior_ml + ((size_t)token * p.nh + head) * 2);
+      if (ml.x != -INFINITY) {
+        const float top = fmaxf(m, ml.x);
+        f.own = m == -INFINITY ? 0.f : exp2f(m - top);
+        f.theirs = exp2f(ml.x - top);
+        f.sum = ml.y * f.theirs;
+        m = top;
+      }
+    }
+  }
+  return f;
+}
+template <bool EXTRAS> __device__ __forceinline__ float prior_value(const Params& p, const PriorFactors& f, int token, int head, int D, int c) {
+  if constexpr (!EXTRAS) return 0.f;
+  return f.theirs > 0.f ? p.prior_acc[((size_t)token * p.nh + head) * D + c] * f.theirs : 0.f;
 }
 template <bool EXTRAS> __device__ __forceinline__ float gate_of(const Params& p, int token, int head, int D, int c) {
   if constexpr (!EXTRAS) return 1.f;
@@ -555,6 +582,9 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
           p.part_ml[item * 2 + 1] = l;
         }
       } else {
+        const PriorFactors pf = prior_of<EXTRAS>(p, token, head, m_all);
+        acc = acc * pf.own + prior_value<EXTRAS>(p, pf, token, head, D, c);
+        l = l * pf.own + pf.sum;
         p.out[(size_t)token * p.out_stride + (size_t)head * D + c] =
             __float2bfloat16_rn(acc / with_sink<EXTRAS>(p, l, m_all) * gate_of<EXTRAS>(p, token, head, D, c));
       }
@@ -609,6 +639,14 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
               acc.w = fmaf(v[j].w, f, acc.w);
             }
           }
+          {
+            const PriorFactors pf = prior_of<EXTRAS>(p, tok0, kvh * g + r, m_ref);
+            l = l * pf.own + pf.sum;
+            acc.x = acc.x * pf.own + prior_value<EXTRAS>(p, pf, tok0, kvh * g + r, D, c);
+            acc.y = acc.y * pf.own + prior_value<EXTRAS>(p, pf, tok0, kvh * g + r, D, c + 1);
+            acc.z = acc.z * pf.own + prior_value<EXTRAS>(p, pf, tok0, kvh * g + r, D, c + 2);
+            acc.w = acc.w * pf.own + prior_value<EXTRAS>(p, pf, tok0, kvh * g + r, D, c + 3);
+          }
           const float inv = 1.f / with_sink<EXTRAS>(p, l, m_ref);
           if (EXTRAS && p.gate) {
             const int head = kvh * g + r;
@@ -630,13 +668,17 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
       const int row = row_start + my_rows + (lane >> 2) + 8 * h;
       if (row >= row_end) continue;
       const int token = tok0 + row / g, head = kvh * g + row % g;
-      const float inv = 1.f / with_sink<EXTRAS>(p, l_run[h], m_run[h]);
+      float m_row = m_run[h];
+      const PriorFactors pf = prior_of<EXTRAS>(p, token, head, m_row);
+      const float inv = 1.f / with_sink<EXTRAS>(p, l_run[h] * pf.own + pf.sum, m_row);
       __nv_bfloat16* dst = p.out + (size_t)token * p.out_stride + (size_t)head * D + (lane & 3) * 2;
 #pragma unroll
       for (int i = 0; i < DTILES; ++i) {
         const int c = i * 8 + (lane & 3) * 2;
-        *reinterpret_cast<unsigned*>(dst + i * 8) = pack_bf16(o_acc[i][2 * h] * inv * gate_of<EXTRAS>(p, token, head, D, c),
-                                                              o_acc[i][2 * h + 1] * inv * gate_of<EXTRAS>(p, token, head, D, c + 1));
+        const float a = o_acc[i][2 * h] * pf.own + prior_value<EXTRAS>(p, pf, token, head, D, c);
+        const float b = o_acc[i][2 * h + 1] * pf.own + prior_value<EXTRAS>(p, pf, token, head, D, c + 1);
+        *reinterpret_cast<unsigned*>(dst + i * 8) = pack_bf16(a * inv * gate_of<EXTRAS>(p, token, head, D, c),
+                                                              b * inv * gate_of<EXTRAS>(p, token, head, D, c + 1));
       }
     }
   }
@@ -654,12 +696,13 @@ attention_combine_kernel(const float* __restrict__ part_acc, const float* __rest
                          const int* __restrict__ tile_req, const int* __restrict__ req_indptr,
                          const int* __restrict__ kv_before, int window,
                          __nv_bfloat16* __restrict__ out, long long out_stride, int nh, int grid_splits, int sink,
-                         const float* __restrict__ gate, long long gate_stride) {
+                         const float* __restrict__ gate, long long gate_stride, const float* __restrict__ prior_ml,
+                         const float* __restrict__ prior_acc) {
   tl::pdl_launch_dependents();  // the next kernel may start its prologue (it waits for us before it reads our output)
   tl::pdl_wait();               // everything before us in the stream is complete and visible
 
   __shared__ float weight[64];
-  __shared__ float total[2];
+  __shared__ float total[3];  // the denominator; the factors of the splits' sums and of the prior's
   const int item = blockIdx.x, c = threadIdx.x;
   const int tile = item / nh, head = item % nh;
   const int req = tile_req ? tile_req[tile] : tile;
@@ -671,16 +714,31 @@ attention_combine_kernel(const float* __restrict__ part_acc, const float* __rest
   if (c < 32) {  // splits <= 64: two per lane
     const float m0 = c < splits ? ml[2 * c] : -INFINITY;
     const float m1 = c + 32 < splits ? ml[2 * (c + 32)] : -INFINITY;
-    const float m_all = tl::warp_max(fmaxf(m0, m1));
-    const float m_ref = m_all == -INFINITY ? 0.f : m_all;
+    float m_all = tl::warp_max(fmaxf(m0, m1));
+    float m_ref = m_all == -INFINITY ? 0.f : m_all;
     const float f0 = c < splits ? exp2f(m0 - m_ref) : 0.f;
     const float f1 = c + 32 < splits ? exp2f(m1 - m_ref) : 0.f;
     weight[c] = f0;
     weight[c + 32] = f1;
     float l = (c < splits ? ml[2 * c + 1] * f0 : 0.f) + (c + 32 < splits ? ml[2 * (c + 32) + 1] * f1 : 0.f);
     l = tl::warp_sum(l);
+    float own = 1.f, theirs = 0.f;
+    if (prior_ml) {
+      const float2 ml2 = *reinterpret_cast<const float2*>(prior_ml + ((size_t)req_indptr[req] * nh + head) * 2);
+      if (ml2.x != -INFINITY) {
+        const float top = fmaxf(m_all, ml2.x);
+        own = m_all == -INFINITY ? 0.f : exp2f(m_all - top);
+        theirs = exp2f(ml2.x - top);
+        l = l * own + ml2.y * theirs;
+        m_all = m_ref = top;
+      }
+    }
     if (sink && m_all != -INFINITY) l += exp2f(-m_ref);  // the sink's share of the denominator
-    if (c == 0) total[0] = l;
+    if (c == 0) {
+      total[0] = l;
+      total[1] = own;
+      total[2] = theirs;
+    }
   }
   __syncthreads();
   const float* src = part_acc + (size_t)item * grid_splits * D + c;
@@ -695,6 +753,7 @@ attention_combine_kernel(const float* __restrict__ part_acc, const float* __rest
   }
   for (; s < splits; ++s) acc = fmaf(src[(size_t)s * D], weight[s], acc);
   const int token = req_indptr[req];
+  if (total[2] > 0.f) acc = acc * total[1] + prior_acc[((size_t)token * nh + head) * D + c] * total[2];
   float result = acc / total[0];
   if (gate) result *= 1.f / (1.f + __expf(-gate[(size_t)token * gate_stride + (size_t)head * D + c]));
   out[(size_t)token * out_stride + (size_t)head * D + c] = __float2bfloat16_rn(result);
@@ -835,13 +894,15 @@ int tl_attention_mma_error() {
 // pages: one cache layer [num_pages][2][nkv][page_size][d].
 // softcap > 0: scores are capped, s <- softcap tanh(s / softcap); sink: one is added to the softmax's
 // denominator; gate (float32 [tokens][gate_stride], or null): the output is multiplied by sigmoid(gate).
+// prior_ml [tokens][nh][2], prior_acc [tokens][nh][d] (float32, or null): a softmax state over other keys that joins
+// every row where it is normalized (max in log2 units of the scaled score, sum, weighted values; max -inf: none).
 int tl_attention_mma_ex(const void* q, long long q_stride, const void* pages, long long num_pages, const int* block_table,
                         int table_width,
                         const int* req_indptr, const int* kv_before, const int* tile_req, const int* tile_row,
                         int tiles, void* out, long long out_stride, int tokens, int nh, int nkv, int d, int page_size,
                         int window, float scale, int rows16, int splits, void* workspace, long long workspace_bytes,
                         int* arrivals, int late_wait, float softcap, int sink, const float* gate, long long gate_stride,
-                        cudaStream_t stream) {
+                        const float* prior_ml, const float* prior_acc, cudaStream_t stream) {
   if (tiles <= 0 || tokens <= 0) return 0;
   if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv || page_size <= 0 || q_stride % 8 || out_stride % 4)
     return TL_ERR_UNSUPPORTED;
@@ -880,8 +941,10 @@ int tl_attention_mma_ex(const void* q, long long q_stride, const void* pages, lo
   p.sink = sink;
   p.gate = gate;
   p.gate_stride = gate_stride;
+  p.prior_ml = prior_acc ? prior_ml : nullptr;
+  p.prior_acc = prior_acc;
   // the plain kernels are compiled without the options, so that they cost a model that has none nothing
-  const bool extras = p.cap_outer > 0.f || p.sink || p.gate;
+  const bool extras = p.cap_outer > 0.f || p.sink || p.gate || p.prior_ml;
   const int rc = d == 128 ? (extras ? launch_for<128, true>(p, num_pages, tiles, rows16 != 0, stream)
                                     : launch_for<128, false>(p, num_pages, tiles, rows16 != 0, stream))
                           : (extras ? launch_for<64, true>(p, num_pages, tiles, rows16 != 0, stream)
@@ -890,10 +953,10 @@ int tl_attention_mma_ex(const void* q, long long q_stride, const void* pages, lo
   const int items = tiles * nh;
   if (d == 128)
     tl::launch_kernel(attention_combine_kernel<128>, items, 128, 0, stream, p.part_acc, p.part_ml, tile_req, req_indptr,
-                      kv_before, window, p.out, out_stride, nh, splits, sink, gate, gate_stride);
+                      kv_before, window, p.out, out_stride, nh, splits, sink, gate, gate_stride, p.prior_ml, p.prior_acc);
   else
     tl::launch_kernel(attention_combine_kernel<64>, items, 64, 0, stream, p.part_acc, p.part_ml, tile_req, req_indptr,
-                      kv_before, window, p.out, out_stride, nh, splits, sink, gate, gate_stride);
+                      kv_before, window, p.out, out_stride, nh, splits, sink, gate, gate_stride, p.prior_ml, p.prior_acc);
   return TL_LAUNCH_CHECK();
 }
 
@@ -905,7 +968,7 @@ int tl_attention_mma(const void* q, long long q_stride, const void* pages, long 
                      int* arrivals, int late_wait, cudaStream_t stream) {
   return tl_attention_mma_ex(q, q_stride, pages, num_pages, block_table, table_width, req_indptr, kv_before, tile_req,
                              tile_row, tiles, out, out_stride, tokens, nh, nkv, d, page_size, window, scale, rows16, splits,
-                             workspace, workspace_bytes, arrivals, late_wait, 0.f, 0, nullptr, 0, stream);
+                             workspace, workspace_bytes, arrivals, late_wait, 0.f, 0, nullptr, 0, nullptr, nullptr, stream);
 }
 
 }  // extern "C"

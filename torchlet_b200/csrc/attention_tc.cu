@@ -81,6 +81,10 @@ struct Params {
   int sink;
   const float* gate;
   long long gate_stride;
+  // a PRIOR softmax state of every (token, head) over keys this kernel does not walk: prior_ml [tokens][nh][2] =
+  // (max in log2 units, sum; max -inf: none), prior_acc [tokens][nh][D] unnormalized; joined where a row is normalized
+  const float* prior_ml;
+  const float* prior_acc;
 };
 
 // tanh by the special-function unit (tanh.approx: relative error 2^-11, which the cap's factor turns into a
@@ -496,6 +500,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
     } else if (num_tiles > 0) {
       mbar_wait(&o_done[x], 0, abort_flag, &g_error_word, 9);
       fence_after_sync();
+      float own = 1.f, theirs = 0.f;
+      const float* prior = nullptr;
+      if (EXTRAS && p.prior_ml && row_valid) {
+        const size_t item = (size_t)(tok0 + row / g) * p.nh + kvh * g + row % g;
+        const float2 ml = *reinterpret_cast<const float2*>(p.prior_ml + item * 2);
+        if (ml.x != -INFINITY) {  // O and the sum stand against m_ref; both sides move to the larger max
+          const float top = fmaxf(m_ref, ml.x);
+          own = m_ref == -INFINITY ? 0.f : exp2f(m_ref - top);
+          theirs = exp2f(ml.x - top);
+          l_sum = l_sum * own + ml.y * theirs;
+          m_ref = top;
+          prior = p.prior_acc + item * D;
+        }
+      }
       if (EXTRAS && p.sink && m_ref != -INFINITY) l_sum += exp2f(-m_ref);  // the sink's share: a key of score 0
       const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
       __nv_bfloat16* dst = nullptr;
@@ -511,7 +529,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
           uint32_t packed[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            float a = __uint_as_float(o[i]) * inv, b = __uint_as_float(o[i + 1]) * inv;
+            float a = __uint_as_float(o[i]), b = __uint_as_float(o[i + 1]);
+            if (EXTRAS && prior) {
+              a = a * own + prior[c + i] * theirs;
+              b = b * own + prior[c + i + 1] * theirs;
+            }
+            a *= inv;
+            b *= inv;
             if (EXTRAS && gate) {
               a *= 1.f / (1.f + __expf(-gate[c + i]));
               b *= 1.f / (1.f + __expf(-gate[c + i + 1]));
@@ -543,7 +567,8 @@ __global__ void __launch_bounds__(128)
 attention_tc_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                           const int* __restrict__ token_req, const int* __restrict__ req_indptr,
                           __nv_bfloat16* __restrict__ out, long long out_stride, int tokens, int nh, int splits, int sink,
-                          const float* __restrict__ gate, long long gate_stride) {
+                          const float* __restrict__ gate, long long gate_stride, const float* __restrict__ prior_ml,
+                          const float* __restrict__ prior_acc) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
   const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -566,6 +591,18 @@ attention_tc_merge_kernel(const float* __restrict__ part_acc, const float* __res
     const float* src = part_acc + ((size_t)item * splits + s) * D + lane * PER;
 #pragma unroll
     for (int i = 0; i < PER; ++i) acc[i] = fmaf(src[i], f, acc[i]);
+  }
+  if (prior_ml) {
+    const float2 ml2 = *reinterpret_cast<const float2*>(prior_ml + (size_t)item * 2);
+    if (ml2.x != -INFINITY) {
+      const float top = fmaxf(m_all, ml2.x);
+      const float own = m_all == -INFINITY ? 0.f : exp2f(m_all - top), theirs = exp2f(ml2.x - top);
+      const float* src = prior_acc + (size_t)item * D + lane * PER;
+      total = total * own + ml2.y * theirs;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) acc[i] = acc[i] * own + src[i] * theirs;
+      m_all = top;
+    }
   }
   if (sink && m_all != -INFINITY) total += exp2f(-m_all);  // the sink's share: a key of score 0
   const float inv = total > 0.f ? 1.f / total : 0.f;
@@ -612,7 +649,7 @@ template <int D>
 int launch_merge(const Params& p, const int* token_req, int tokens, cudaStream_t stream) {
   tl::launch_kernel(attention_tc_merge_kernel<D>, (tokens * p.nh + 3) / 4, 128, 0, stream, (const float*)p.part_acc,
                     (const float*)p.part_ml, token_req, p.req_indptr, p.out, p.out_stride, tokens, p.nh, p.splits, p.sink,
-                    p.gate, p.gate_stride);
+                    p.gate, p.gate_stride, p.prior_ml, p.prior_acc);
   return TL_LAUNCH_CHECK();
 }
 
@@ -665,7 +702,8 @@ int tl_attention_tc(const void* q, long long q_stride, const void* pages, long l
                     const int* tile_req, const int* tile_row, int tiles, void* out, long long out_stride, int nh,
                     int nkv, int d, int page_size, int window, float scale, int splits, const int* token_req,
                     int tokens, void* workspace, long long workspace_bytes, int defer_merge, float softcap, int sink,
-                    const float* gate, long long gate_stride, cudaStream_t stream) {
+                    const float* gate, long long gate_stride, const float* prior_ml, const float* prior_acc,
+                    cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (splits < 1 || splits > 64) return TL_ERR_UNSUPPORTED;
   if (splits > 1 && (!token_req || tokens <= 0 || !workspace ||
@@ -699,12 +737,14 @@ int tl_attention_tc(const void* q, long long q_stride, const void* pages, long l
   p.sink = sink;
   p.gate = gate;
   p.gate_stride = gate_stride;
+  p.prior_ml = prior_acc ? prior_ml : nullptr;
+  p.prior_acc = prior_acc;
   p.splits = splits;
   p.part_acc = (float*)workspace;
   p.part_ml = p.part_acc + (size_t)(splits > 1 ? tokens : 0) * nh * splits * d;
   // the plain kernels are compiled without the options, so that they cost a model that has none nothing
   const bool merge_later = defer_merge != 0;
-  if (p.cap_outer > 0.f || p.sink || p.gate)
+  if (p.cap_outer > 0.f || p.sink || p.gate || p.prior_ml)
     return d == 128 ? launch<128, true>(map_kv, p, nkv, tiles, token_req, tokens, merge_later, stream)
                     : launch<64, true>(map_kv, p, nkv, tiles, token_req, tokens, merge_later, stream);
   return d == 128 ? launch<128, false>(map_kv, p, nkv, tiles, token_req, tokens, merge_later, stream)
@@ -715,7 +755,8 @@ int tl_attention_tc(const void* q, long long q_stride, const void* pages, long l
 // token_req and workspace as that call.
 int tl_attention_tc_merge(const int* req_indptr, void* out, long long out_stride, int nh, int d, int splits,
                           const int* token_req, int tokens, void* workspace, long long workspace_bytes, int sink,
-                          const float* gate, long long gate_stride, cudaStream_t stream) {
+                          const float* gate, long long gate_stride, const float* prior_ml, const float* prior_acc,
+                          cudaStream_t stream) {
   if (splits <= 1 || tokens <= 0) return 0;
   if ((d != 64 && d != 128) || !token_req || !workspace || out_stride % 8 ||
       workspace_bytes < tl_attention_tc_workspace(tokens, nh, d, splits))
@@ -730,6 +771,8 @@ int tl_attention_tc_merge(const int* req_indptr, void* out, long long out_stride
   p.sink = sink;
   p.gate = gate;
   p.gate_stride = gate_stride;
+  p.prior_ml = prior_acc ? prior_ml : nullptr;
+  p.prior_acc = prior_acc;
   p.part_acc = (float*)workspace;
   p.part_ml = p.part_acc + (size_t)tokens * nh * splits * d;
   return d == 128 ? launch_merge<128>(p, token_req, tokens, stream) : launch_merge<64>(p, token_req, tokens, stream);

@@ -5,9 +5,11 @@
 //                              the blocks b with b P + P - 1 <= i - size   (nb(i) = floor((i - size + 1) / P) of them),
 //   a block's key / value being the mean of its P cached keys / values.
 //
-// Keys may be wider or narrower than values (d, dv).  A token keeps ONE cache row per KV head, [key (d) | value (dv)],
-// in pages [num_pages, 1, kv heads, page_size, d + dv] of the storage type T; pooled rows are float32 and live in
-// the request's slot, pooled[slot, block, kv head, d + dv] (a slot has room for the engine's longest sequence).
+// Keys may be wider or narrower than values (d, dv).  A token's cache rows are in pages of the storage type T, in one
+// of two layouts: JOINED, one row per KV head, [key (d) | value (dv)], pages [num_pages, 1, kv heads, page_size, d + dv];
+// or, where d = dv, SPLIT into a key plane and a value plane, pages [num_pages, 2, kv heads, page_size, d], which is
+// what the tensor-core attention kernels read.  Pooled rows are float32 and live in the request's slot,
+// pooled[slot, block, kv head, d + dv] (a slot has room for the engine's longest sequence).
 //
 // Kernels:
 //   store      one block a token: its key and value rows go to its page; the token that completes a block
@@ -17,6 +19,9 @@
 //   attention  one warp a (token, query head): pooled rows in tiles of 32 blocks, then the window's tokens in tiles
 //              of 32 ABSOLUTE positions, online softmax, float32 throughout; the order of every sum depends on the
 //              position alone.  The true 32-bit kernel and the any-size kernel of the bfloat16 engine.
+//   prior      one warp a (token, query head): the softmax state over the pooled rows ALONE (max in log2 units of the
+//              scaled score, sum, unnormalized weighted values, float32), which the tensor-core kernels that walk the
+//              window's tokens (attention_mma.cu, attention_tc.cu) join where they normalize a row.
 #include <math.h>
 
 #include "common.cuh"
@@ -28,15 +33,31 @@ using namespace tl;
 constexpr int WARPS = 4;
 constexpr int MAX_D = 256;
 
+// Where the rows of (page, KV head, place in the page) start, in elements.
+struct Layout {
+  size_t page_stride, v_base;
+  int row;
+  __device__ Layout(int split, int nkv, int d, int dv, int page_size) {
+    row = split ? d : d + dv;
+    page_stride = (size_t)(split ? 2 : 1) * nkv * page_size * row;
+    v_base = split ? (size_t)nkv * page_size * d : (size_t)d;
+  }
+  __device__ size_t key(int page, int g, int place, int page_size) const {
+    return (size_t)page * page_stride + ((size_t)g * page_size + place) * row;
+  }
+  __device__ size_t value(int page, int g, int place, int page_size) const { return key(page, g, place, page_size) + v_base; }
+};
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 pooled_store_kernel(const T* __restrict__ proj, int proj_stride, int k_offset, int v_offset, T* __restrict__ pages,
                     const int* __restrict__ block_table, int table_width, const int* __restrict__ token_req,
                     const int* __restrict__ positions, const int* __restrict__ req_indptr,
                     const int* __restrict__ slots, float* __restrict__ pooled, int max_blocks, int max_slots, int nkv,
-                    int d, int dv, int page_size, int pool, int num_pages) {
+                    int d, int dv, int page_size, int pool, int num_pages, int split) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
+  const Layout at(split, nkv, d, dv, page_size);
   const int t = blockIdx.x;
   const int req = token_req[t], pos = positions[t];
   const int row = d + dv;
@@ -47,8 +68,10 @@ pooled_store_kernel(const T* __restrict__ proj, int proj_stride, int k_offset, i
   const T* mine = proj + (size_t)t * proj_stride;
   for (int e = threadIdx.x; e < nkv * row; e += blockDim.x) {
     const int g = e / row, c = e - g * row;
-    const T v = c < d ? mine[k_offset + g * d + c] : mine[v_offset + g * dv + (c - d)];
-    pages[(((size_t)page * nkv + g) * page_size + pos % page_size) * row + c] = v;
+    if (c < d)
+      pages[at.key(page, g, pos % page_size, page_size) + c] = mine[k_offset + g * d + c];
+    else
+      pages[at.value(page, g, pos % page_size, page_size) + (c - d)] = mine[v_offset + g * dv + (c - d)];
   }
   if ((pos + 1) % pool) return;
   const int slot = slots[req];
@@ -71,7 +94,8 @@ pooled_store_kernel(const T* __restrict__ proj, int proj_stride, int k_offset, i
         int pg = 0;
         if (TL_DEBUG_OK(p / page_size < table_width, TL_DEBUG_POSITION, p)) pg = table[p / page_size];
         if (!TL_DEBUG_OK(pg >= 0 && pg < num_pages, TL_DEBUG_PAGE, pg)) pg = 0;
-        v = to_float(pages[(((size_t)pg * nkv + g) * page_size + p % page_size) * row + c]);
+        v = to_float(c < d ? pages[at.key(pg, g, p % page_size, page_size) + c]
+                           : pages[at.value(pg, g, p % page_size, page_size) + (c - d)]);
       }
       sum += v;
     }
@@ -86,9 +110,10 @@ pooled_attention_kernel(const T* __restrict__ q, int q_stride, const T* __restri
                         const int* __restrict__ positions, const int* __restrict__ slots,
                         const float* __restrict__ pooled, int max_blocks, int max_slots, T* __restrict__ out,
                         int out_stride, int tokens, int nh, int nkv, int d, int dv, int page_size, int size, int pool,
-                        float scale, int num_pages) {
+                        float scale, int num_pages, int split) {
   tl::pdl_wait();
   tl::pdl_launch_dependents();
+  const Layout at(split, nkv, d, dv, page_size);
   __shared__ float qs[WARPS][MAX_D];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -155,7 +180,7 @@ pooled_attention_kernel(const T* __restrict__ q, int q_stride, const T* __restri
       int page = 0;
       if (TL_DEBUG_OK(key / page_size < table_width, TL_DEBUG_POSITION, key)) page = table[key / page_size];
       if (!TL_DEBUG_OK(page >= 0 && page < num_pages, TL_DEBUG_PAGE, page)) page = 0;
-      row_off = (((size_t)page * nkv + kvh) * page_size + key % page_size) * row;
+      row_off = at.key(page, kvh, key % page_size, page_size);
       const T* krow = pages + row_off;
       float dot = 0.f;
       for (int i = 0; i < d; ++i) dot = fmaf(qs[warp][i], to_float(krow[i]), dot);
@@ -173,7 +198,7 @@ pooled_attention_kernel(const T* __restrict__ q, int q_stride, const T* __restri
     for (int j = first; j <= last; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const size_t off = __shfl_sync(0xffffffffu, (unsigned long long)row_off, j);
-      const T* vrow = pages + off + d;
+      const T* vrow = pages + off + at.v_base;
 #pragma unroll
       for (int c = 0; c < MAX_D / 32; ++c) {
         const int i = lane + 32 * c;
@@ -190,38 +215,128 @@ pooled_attention_kernel(const T* __restrict__ q, int q_stride, const T* __restri
   }
 }
 
+// The softmax state of every (token, query head) over its pooled rows alone.  ml[item] = (max, sum) with the max in
+// log2 units (score * scale * log2 e), acc[item][dv] = sum_b 2^(s_b - max) value_b; a row that sees no block: (-inf, 0).
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32)
+pooled_prior_kernel(const T* __restrict__ q, int q_stride, const int* __restrict__ token_req,
+                    const int* __restrict__ positions, const int* __restrict__ slots, const float* __restrict__ pooled,
+                    int max_blocks, int max_slots, float* __restrict__ ml, float* __restrict__ acc_out, int tokens, int nh,
+                    int nkv, int d, int dv, int size, int pool, float scale_log2) {
+  tl::pdl_wait();
+  tl::pdl_launch_dependents();
+  __shared__ float qs[WARPS][MAX_D];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * WARPS + warp;
+  if (item >= (long long)tokens * nh) return;
+  const int t = (int)(item / nh), h = (int)(item % nh);
+  const int kvh = h / (nh / nkv);
+  const int pos = positions[t];
+  const int slot = slots[token_req[t]];
+  const bool live = TL_DEBUG_OK(slot >= -1 && slot < max_slots, TL_DEBUG_SLOT, slot) && slot >= 0;
+  int blocks = (live && pos - size + 1 > 0) ? (pos - size + 1) / pool : 0;
+  if (blocks > max_blocks) blocks = max_blocks;
+  if (blocks == 0) {
+    if (lane == 0) {
+      ml[item * 2] = -INFINITY;
+      ml[item * 2 + 1] = 0.f;
+    }
+    return;
+  }
+  const int row = d + dv;
+  const T* qrow = q + (size_t)t * q_stride + (size_t)h * d;
+  for (int i = lane; i < d; i += 32) qs[warp][i] = to_float(qrow[i]);
+  __syncwarp();
+  float m = -INFINITY, l = 0.f;
+  float acc[MAX_D / 32];
+#pragma unroll
+  for (int c = 0; c < MAX_D / 32; ++c) acc[c] = 0.f;
+  const float* mine = pooled + ((size_t)slot * max_blocks * nkv + kvh) * row;
+  for (int start = 0; start < blocks; start += 32) {
+    const int b = start + lane;
+    const bool valid = b < blocks;
+    float s = -INFINITY;
+    if (valid) {
+      const float4* krow = reinterpret_cast<const float4*>(mine + (size_t)b * nkv * row);
+      float dot = 0.f;
+      if ((row & 3) == 0 && (d & 3) == 0) {
+        for (int i = 0; i < d / 4; ++i) {
+          const float4 k4 = krow[i];
+          dot = fmaf(qs[warp][4 * i], k4.x, dot);
+          dot = fmaf(qs[warp][4 * i + 1], k4.y, dot);
+          dot = fmaf(qs[warp][4 * i + 2], k4.z, dot);
+          dot = fmaf(qs[warp][4 * i + 3], k4.w, dot);
+        }
+      } else {
+        const float* k1 = mine + (size_t)b * nkv * row;
+        for (int i = 0; i < d; ++i) dot = fmaf(qs[warp][i], k1[i], dot);
+      }
+      s = dot * scale_log2;
+    }
+    const float new_m = fmaxf(m, warp_max(s));
+    const float corr = exp2f(m - new_m);
+    const float p = valid ? exp2f(s - new_m) : 0.f;
+    l = l * corr + warp_sum(p);
+    m = new_m;
+#pragma unroll
+    for (int c = 0; c < MAX_D / 32; ++c) acc[c] *= corr;
+    const int last = blocks - start < 32 ? blocks - start : 32;
+    for (int j = 0; j < last; ++j) {
+      const float pj = __shfl_sync(0xffffffffu, p, j);
+      const float* vrow = mine + (size_t)(start + j) * nkv * row + d;
+#pragma unroll
+      for (int c = 0; c < MAX_D / 32; ++c) {
+        const int i = lane + 32 * c;
+        if (i < dv) acc[c] = fmaf(pj, vrow[i], acc[c]);
+      }
+    }
+  }
+  if (lane == 0) {
+    ml[item * 2] = m;
+    ml[item * 2 + 1] = l;
+  }
+  float* dst = acc_out + (size_t)item * dv;
+#pragma unroll
+  for (int c = 0; c < MAX_D / 32; ++c) {
+    const int i = lane + 32 * c;
+    if (i < dv) dst[i] = acc[c];
+  }
+}
+
 }  // namespace
 
 TL_DEBUG_READER(tl_pooled_attention_debug_error)
 
 extern "C" {
 
-// proj rows hold the keys at k_offset (nkv x d) and the values at v_offset (nkv x dv).
+// proj rows hold the keys at k_offset (nkv x d) and the values at v_offset (nkv x dv).  split != 0: the pages are
+// [num_pages, 2, nkv, page_size, d] (d = dv), else [num_pages, 1, nkv, page_size, d + dv].
 int tl_pooled_store(const void* proj, int proj_stride, int k_offset, int v_offset, void* pages, int dtype,
                     const int* block_table, int table_width, const int* token_req, const int* positions,
                     const int* req_indptr, const int* slots, float* pooled, int max_blocks, int max_slots, int tokens,
-                    int nkv, int d, int dv, int page_size, int pool, int num_pages, cudaStream_t stream) {
+                    int nkv, int d, int dv, int page_size, int pool, int num_pages, int split, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (nkv <= 0 || d <= 0 || dv <= 0 || page_size <= 0 || pool <= 0) return TL_ERR_UNSUPPORTED;
+  if (nkv <= 0 || d <= 0 || dv <= 0 || page_size <= 0 || pool <= 0 || (split && d != dv)) return TL_ERR_UNSUPPORTED;
   if (dtype == TL_DTYPE_F32)
     tl::launch_kernel(pooled_store_kernel<float>, (unsigned)tokens, 128, 0, stream, (const float*)proj, proj_stride,
                       k_offset, v_offset, (float*)pages, block_table, table_width, token_req, positions, req_indptr,
-                      slots, pooled, max_blocks, max_slots, nkv, d, dv, page_size, pool, num_pages);
+                      slots, pooled, max_blocks, max_slots, nkv, d, dv, page_size, pool, num_pages, split);
   else
     tl::launch_kernel(pooled_store_kernel<__nv_bfloat16>, (unsigned)tokens, 128, 0, stream,
                       (const __nv_bfloat16*)proj, proj_stride, k_offset, v_offset, (__nv_bfloat16*)pages, block_table,
                       table_width, token_req, positions, req_indptr, slots, pooled, max_blocks, max_slots, nkv, d, dv,
-                      page_size, pool, num_pages);
+                      page_size, pool, num_pages, split);
   return TL_LAUNCH_CHECK();
 }
 
 int tl_pooled_attention(const void* q, int q_stride, const void* pages, int dtype, const int* block_table,
                         int table_width, const int* token_req, const int* positions, const int* slots,
                         const float* pooled, int max_blocks, int max_slots, void* out, int out_stride, int tokens, int nh,
-                        int nkv, int d, int dv, int page_size, int size, int pool, float scale, int num_pages,
+                        int nkv, int d, int dv, int page_size, int size, int pool, float scale, int num_pages, int split,
                         cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (d <= 0 || d > MAX_D || dv <= 0 || dv > MAX_D || nkv <= 0 || nh % nkv || page_size <= 0 || size <= 0 || pool < 0)
+  if (d <= 0 || d > MAX_D || dv <= 0 || dv > MAX_D || nkv <= 0 || nh % nkv || page_size <= 0 || size <= 0 || pool < 0 ||
+      (split && d != dv))
     return TL_ERR_UNSUPPORTED;
   const long long items = (long long)tokens * nh;
   const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
@@ -229,12 +344,34 @@ int tl_pooled_attention(const void* q, int q_stride, const void* pages, int dtyp
     tl::launch_kernel(pooled_attention_kernel<float>, blocks, WARPS * 32, 0, stream, (const float*)q, q_stride,
                       (const float*)pages, block_table, table_width, token_req, positions, slots, pooled, max_blocks,
                       max_slots, (float*)out, out_stride, tokens, nh, nkv, d, dv, page_size, size, pool, scale,
-                      num_pages);
+                      num_pages, split);
   else
     tl::launch_kernel(pooled_attention_kernel<__nv_bfloat16>, blocks, WARPS * 32, 0, stream, (const __nv_bfloat16*)q,
                       q_stride, (const __nv_bfloat16*)pages, block_table, table_width, token_req, positions, slots,
                       pooled, max_blocks, max_slots, (__nv_bfloat16*)out, out_stride, tokens, nh, nkv, d, dv, page_size,
-                      size, pool, scale, num_pages);
+                      size, pool, scale, num_pages, split);
+  return TL_LAUNCH_CHECK();
+}
+
+// The softmax state over the pooled rows alone, for the kernels that walk the window's tokens: ml [tokens][nh][2],
+// acc [tokens][nh][dv], float32.
+int tl_pooled_prior(const void* q, int q_stride, int dtype, const int* token_req, const int* positions, const int* slots,
+                    const float* pooled, int max_blocks, int max_slots, float* ml, float* acc, int tokens, int nh, int nkv,
+                    int d, int dv, int size, int pool, float scale, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (d <= 0 || d > MAX_D || dv <= 0 || dv > MAX_D || nkv <= 0 || nh % nkv || size <= 0 || pool <= 0)
+    return TL_ERR_UNSUPPORTED;
+  const long long items = (long long)tokens * nh;
+  const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  if (dtype == TL_DTYPE_F32)
+    tl::launch_kernel(pooled_prior_kernel<float>, blocks, WARPS * 32, 0, stream, (const float*)q, q_stride, token_req,
+                      positions, slots, pooled, max_blocks, max_slots, ml, acc, tokens, nh, nkv, d, dv, size, pool,
+                      scale_log2);
+  else
+    tl::launch_kernel(pooled_prior_kernel<__nv_bfloat16>, blocks, WARPS * 32, 0, stream, (const __nv_bfloat16*)q, q_stride,
+                      token_req, positions, slots, pooled, max_blocks, max_slots, ml, acc, tokens, nh, nkv, d, dv, size,
+                      pool, scale_log2);
   return TL_LAUNCH_CHECK();
 }
 

@@ -68,7 +68,7 @@ _SIGNATURES = {
         "tl_attention_mma_ex": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                 c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_float, c_int, c_void_p, c_longlong,
-                                c_void_p],
+                                c_void_p, c_void_p, c_void_p],
         "tl_attention_mma_error": [],
         "tl_attention_mma_debug_error": [c_void_p],
     },
@@ -83,9 +83,9 @@ _SIGNATURES = {
         "tl_attention_tc": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_float,
                             c_int, c_void_p, c_int, c_void_p, c_longlong, c_int, c_float, c_int, c_void_p, c_longlong,
-                            c_void_p],
+                            c_void_p, c_void_p, c_void_p],
         "tl_attention_tc_merge": [c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
-                                  c_longlong, c_int, c_void_p, c_longlong, c_void_p],
+                                  c_longlong, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p],
         "tl_attention_tc_error": [],
         "tl_attention_tc_rows": [c_int],
     },
@@ -173,10 +173,13 @@ _SIGNATURES = {
     },
     "pooled_attention": {
         "tl_pooled_store": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_void_p],
         "tl_pooled_attention": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                c_float, c_int, c_void_p],
+                                c_float, c_int, c_int, c_void_p],
+        "tl_pooled_prior": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
         "tl_pooled_attention_debug_error": [c_void_p],
     },
     "sampling": {
@@ -611,18 +614,28 @@ def hyper_write(z, y, mix, b) -> None:
 def pooled_store(proj, k_offset: int, v_offset: int, pages, block_table, token_req, positions, req_indptr, slots, pooled,
                  nkv: int, d: int, dv: int, page_size: int, pool: int) -> None:
     """The step's keys and values (``proj[:, k_offset:]``: nkv x d, ``proj[:, v_offset:]``: nkv x dv) into the
-    pages' rows [key | value]; a token that completes a block of ``pool`` tokens also writes the block's mean row
-    into ``pooled`` [slots, blocks, nkv, d + dv] (float32) of its request's slot (csrc/pooled_attention.cu)."""
+    pages (one plane of rows [key | value], or a key plane and a value plane where d = dv); a token that completes a
+    block of ``pool`` tokens also writes the block's mean row into ``pooled`` [slots, blocks, nkv, d + dv] (float32)
+    of its request's slot (csrc/pooled_attention.cu)."""
     _need_cuda(proj, pages, block_table, token_req, positions, req_indptr, slots, pooled)
     assert pages.dtype == proj.dtype and proj.stride(1) == 1 and pages.is_contiguous() and pooled.is_contiguous()
     assert pooled.dtype == torch.float32 and pooled.shape[2:] == (nkv, d + dv)
-    assert pages.shape[1:] == (1, nkv, page_size, d + dv)
+    split = _pooled_split(pages, nkv, d, dv, page_size)
     code = _fn("pooled_attention", "tl_pooled_store")(
         proj.data_ptr(), proj.stride(0), k_offset, v_offset, pages.data_ptr(), dtype_code(proj.dtype),
         block_table.data_ptr(), block_table.shape[1], token_req.data_ptr(), positions.data_ptr(), req_indptr.data_ptr(),
         slots.data_ptr(), pooled.data_ptr(), pooled.shape[1], pooled.shape[0], proj.shape[0], nkv, d, dv, page_size, pool,
-        pages.shape[0], _stream())
+        pages.shape[0], split, _stream())
     _check(code, "pooled_store")
+
+
+def _pooled_split(pages, nkv: int, d: int, dv: int, page_size: int) -> int:
+    """1: the pages hold a key plane and a value plane; 0: one plane of joined rows."""
+    if pages.shape[1] == 2:
+        assert d == dv and pages.shape[1:] == (2, nkv, page_size, d)
+        return 1
+    assert pages.shape[1:] == (1, nkv, page_size, d + dv)
+    return 0
 
 
 def pooled_attention(q, pages, block_table, token_req, positions, slots, pooled, out, nh: int, nkv: int, d: int, dv: int,
@@ -637,8 +650,26 @@ def pooled_attention(q, pages, block_table, token_req, positions, slots, pooled,
         q.data_ptr(), q.stride(0), pages.data_ptr(), dtype_code(q.dtype), block_table.data_ptr(), block_table.shape[1],
         token_req.data_ptr(), positions.data_ptr(), slots.data_ptr(), pooled.data_ptr(), pooled.shape[1], pooled.shape[0],
         out.data_ptr(), out.stride(0), tokens, nh, nkv, d, dv, page_size, size, pool, float(scale), pages.shape[0],
-        _stream())
+        _pooled_split(pages, nkv, d, dv, page_size), _stream())
     _check(code, "pooled_attention")
+
+
+def pooled_prior(q, token_req, positions, slots, pooled, ml, acc, nh: int, nkv: int, d: int, dv: int, size: int,
+                 pool: int, scale: float) -> None:
+    """The softmax state of every (token, head) over the pooled rows of the whole blocks before its window, alone:
+    ``ml`` [tokens, nh, 2] = (max in log2 units of the scaled score, sum; (-inf, 0) where no block is seen), ``acc``
+    [tokens, nh, dv] the unnormalized weighted values, float32.  ``attention_mma`` and ``attention_tc`` take the two
+    as their ``prior``."""
+    _need_cuda(q, token_req, positions, slots, pooled, ml, acc)
+    tokens = q.shape[0]
+    assert q.stride(1) == 1 and pooled.dtype == ml.dtype == acc.dtype == torch.float32
+    assert pooled.is_contiguous() and ml.is_contiguous() and acc.is_contiguous()
+    assert ml.shape == (tokens, nh, 2) and acc.shape == (tokens, nh, dv) and pooled.shape[2:] == (nkv, d + dv)
+    code = _fn("pooled_attention", "tl_pooled_prior")(
+        q.data_ptr(), q.stride(0), dtype_code(q.dtype), token_req.data_ptr(), positions.data_ptr(), slots.data_ptr(),
+        pooled.data_ptr(), pooled.shape[1], pooled.shape[0], ml.data_ptr(), acc.data_ptr(), tokens, nh, nkv, d, dv, size,
+        pool, float(scale), _stream())
+    _check(code, "pooled_prior")
 
 
 # ------------------------------------------------------- routed feed-forward
@@ -1025,7 +1056,7 @@ _merge_in_kernel = os.environ.get("TORCHLET_B200_DECODE_MERGE", "") != "kernel"
 
 def attention_mma(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, tiles, out, tokens, nh, nkv,
                   d, page_size, window, scale, rows16: bool, splits: int = 1, late_wait: bool = False,
-                  softcap=None, sink: bool = False, gate=None) -> None:
+                  softcap=None, sink: bool = False, gate=None, prior=None) -> None:
     """Tensor-core paged attention (csrc/attention_mma.cu).  ``tile_req``/``tile_row`` None:
     tile i is request i from its first packed row.  With ``splits`` > 1 every tile is a request
     that brings one token; only those tokens' rows of ``out`` are written.  ``splits`` is the
@@ -1034,8 +1065,11 @@ def attention_mma(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile
     stream was ``attention_tc`` for the other requests of the same step; this grid starts beside
     it and waits for it at its end instead of at its start.  ``softcap``: scores become
     softcap * tanh(score / softcap); ``sink``: one is added to the softmax's denominator; ``gate`` (float32
-    rows [tokens, >= nh * d]): the output is multiplied by sigmoid(gate)."""
+    rows [tokens, >= nh * d]): the output is multiplied by sigmoid(gate).  ``prior`` = (ml [tokens, nh, 2], acc
+    [tokens, nh, d]), float32: a softmax state over keys the kernel does not walk (``pooled_prior``), joined with every
+    row's own where the row is normalized."""
     _need_cuda(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, out, gate)
+    prior_ml, prior_acc = _prior(prior, qkv.shape[0], nh, d)
     assert qkv.dtype == pages.dtype == out.dtype == torch.bfloat16
     assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1)
     # key splits: float32 partial results of every (decode tile, head, split); the split that finishes last merges
@@ -1051,8 +1085,19 @@ def attention_mma(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile
         out.data_ptr(), out.stride(0), tokens, nh, nkv, d, page_size, int(window or 0), float(scale),
         1 if rows16 else 0, splits,
         _ptr(ws), ws.numel() * 4 if ws is not None else 0, _ptr(arrivals), 1 if late_wait else 0,
-        float(softcap or 0.0), 1 if sink else 0, _ptr(gate), gate.stride(0) if gate is not None else 0, _stream())
+        float(softcap or 0.0), 1 if sink else 0, _ptr(gate), gate.stride(0) if gate is not None else 0,
+        _ptr(prior_ml), _ptr(prior_acc), _stream())
     _check(code, "attention_mma", 2 if splits > 1 and arrivals is None else 1)
+
+
+def _prior(prior, tokens: int, nh: int, d: int):
+    if prior is None:
+        return None, None
+    ml, acc = prior
+    _need_cuda(ml, acc)
+    assert ml.dtype == acc.dtype == torch.float32 and ml.is_contiguous() and acc.is_contiguous()
+    assert ml.shape == (tokens, nh, 2) and acc.shape == (tokens, nh, d)
+    return ml, acc
 
 
 def attention_tc_rows(group: int) -> int:
@@ -1066,19 +1111,21 @@ def attention_tc_supported(d: int, group: int, page_size: int) -> bool:
 
 def attention_tc(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, tiles, out, nh, nkv, d,
                  page_size, window, scale, splits: int = 1, token_req=None, defer_merge: bool = False,
-                 softcap=None, sink: bool = False, gate=None):
+                 softcap=None, sink: bool = False, gate=None, prior=None):
     """Prompt-portion attention on tcgen05 (csrc/attention_tc.cu): tiles of packed rows
     (``tile_row`` multiples of ``attention_tc_rows(nh // nkv)``) that cover every request of the
     step with more than one token.  ``splits`` > 1: that many CTAs share the key tiles of each
     (row tiles, KV head) and a second kernel merges them (``token_req``: each token's request).
     ``defer_merge``: that second kernel is not launched; the call returns a function that launches
     it (None when there is nothing to merge), so that the decode attention may run between the two.
-    The partial results have a workspace of their own.  ``softcap``, ``sink``, ``gate``: as in ``attention_mma``."""
+    The partial results have a workspace of their own.  ``softcap``, ``sink``, ``gate``, ``prior``: as in
+    ``attention_mma``."""
     _need_cuda(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, out, token_req, gate)
     assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1)
     gate_stride = gate.stride(0) if gate is not None else 0
     assert qkv.dtype == pages.dtype == out.dtype == torch.bfloat16 and pages.is_contiguous()
     tokens = qkv.shape[0]
+    prior_ml, prior_acc = _prior(prior, tokens, nh, d)
     need = tokens * nh * splits * (d + 2) * 4 if splits > 1 else 0
     ws = _workspace(("attention_tc", qkv.device), need) if need else None
     ws_bytes = ws.numel() * 4 if ws is not None else 0
@@ -1088,7 +1135,7 @@ def attention_tc(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_
         block_table.shape[1], req_indptr.data_ptr(), kv_before.data_ptr(), tile_req.data_ptr(), tile_row.data_ptr(),
         tiles, out.data_ptr(), out.stride(0), nh, nkv, d, page_size, int(window or 0), float(scale), splits,
         _ptr(token_req), tokens, _ptr(ws), ws_bytes, 1 if defer else 0, float(softcap or 0.0), 1 if sink else 0,
-        _ptr(gate), gate_stride, _stream())
+        _ptr(gate), gate_stride, _ptr(prior_ml), _ptr(prior_acc), _stream())
     _check(code, "attention_tc", 2 if splits > 1 and not defer else 1)
     if not defer:
         return None
@@ -1096,7 +1143,8 @@ def attention_tc(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_
     def merge() -> None:
         code = _fn("attention_tc", "tl_attention_tc_merge")(
             req_indptr.data_ptr(), out.data_ptr(), out.stride(0), nh, d, splits, token_req.data_ptr(), tokens,
-            ws.data_ptr(), ws_bytes, 1 if sink else 0, _ptr(gate), gate_stride, _stream())
+            ws.data_ptr(), ws_bytes, 1 if sink else 0, _ptr(gate), gate_stride, _ptr(prior_ml), _ptr(prior_acc),
+            _stream())
         _check(code, "attention_tc_merge", 1)
 
     return merge

@@ -117,10 +117,11 @@ def _plan(ctx, group_size: int, rows_per_tile: int = ROWS):
     return plan
 
 
-def forward(mixer, ctx, qkv, cache, out, gate=None) -> bool:
+def forward(mixer, ctx, qkv, cache, out, gate=None, prior=None) -> bool:
     """``qkv``: rows whose first ``nh * d`` entries are the (encoded) queries; keys and values are in
     the cache pages.  A mixer's score cap (``mixer.softcap``), sink (``mixer.sink``) and output ``gate``
-    (float32 rows) are arguments of all three kernels."""
+    (float32 rows) are arguments of all three kernels; ``prior`` (a softmax state of every (token, head) over
+    keys that are not in the pages, ``ops.pooled_prior``) of the two tensor-core kernels."""
     d, nh, nkv = mixer.head_dim, mixer.num_heads, mixer.num_kv_heads
     group = nh // nkv
     if d not in (64, 128) or group > 16 or qkv.stride(0) % 8:
@@ -130,7 +131,7 @@ def forward(mixer, ctx, qkv, cache, out, gate=None) -> bool:
     use_tc = (not ctx.decode_only) and ops.attention_tc_supported(d, group, cache.page_size)
     plan = _plan(ctx, group, ops.attention_tc_rows(group) if use_tc else ROWS)
     common = dict(out=out, tokens=ctx.num_tokens, nh=nh, nkv=nkv, d=d, page_size=cache.page_size,
-                  window=mixer.window, scale=mixer.scale, softcap=softcap, sink=sink, gate=gate)
+                  window=mixer.window, scale=mixer.scale, softcap=softcap, sink=sink, gate=gate, prior=prior)
     # A mixed step: the prompt portions first (few CTAs that walk long contexts), the decoding
     # requests' kernel right behind it on the SMs it leaves idle; the two touch different rows.
     merge_portions, beside = None, False
@@ -141,7 +142,7 @@ def forward(mixer, ctx, qkv, cache, out, gate=None) -> bool:
         merge_portions = ops.attention_tc(
             qkv, cache.pages, cache.block_table, ctx.req_indptr, ctx.kv_before, tile_req, tile_row, count, out, nh, nkv,
             d, cache.page_size, mixer.window, mixer.scale, splits=splits, token_req=ctx.token_req, defer_merge=beside,
-            softcap=softcap, sink=sink, gate=gate)
+            softcap=softcap, sink=sink, gate=gate, prior=prior)
     if plan["decode"] is not None:
         tile_req, count = plan["decode"]
         splits = decode_splits(count, nkv, ctx.max_kv_len, qkv.device)

@@ -8,9 +8,11 @@ Tokens that have left the window while their block is not yet complete and passe
 share one softmax of (q . k) * ``scale``; query head h reads KV head h // (heads / kv_heads); the heads,
 concatenated, go through W_o (+ b_o) into the stream.
 
-What the mixer keeps: one cache row [key | value] a token and KV head in pages, held while the token is inside the
-window or its block is incomplete (a windowed page group of max(window, pool) tokens), and the pooled rows, float32,
-in the request's slot: one a block, written by the step that brings the block's last token (csrc/pooled_attention.cu).
+What the mixer keeps: a token's key and value per KV head in pages (one joined row [key | value]; a key plane and a
+value plane where the two are equally wide and the tensor-core kernels take the size), held while the token is inside
+the window or its block is incomplete (a windowed page group of max(window, pool) tokens), and the pooled rows,
+float32, in the request's slot: one a block, written by the step that brings the block's last token
+(csrc/pooled_attention.cu).
 
 Parameters: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``v_dim``, ``scale``, ``window``, ``pool``,
 ``bias`` (default True: q, k, v and o have biases).  Tensors below the prefix: q [H D, hidden], k [G D, hidden],
@@ -57,6 +59,10 @@ class PooledWindowAttention(Mixer):
 
     def kv_spec(self) -> KVSpec:
         # a token's row is needed while it is in the window, and until the token that completes its block has come
+        from .pooled_attention_bf16 import split_planes
+
+        if split_planes(self.head_dim, self.v_dim):
+            return KVSpec(self.num_kv_heads, self.head_dim, max(self.window, self.pool), planes=2)
         return KVSpec(self.num_kv_heads, self.head_dim + self.v_dim, max(self.window, self.pool), planes=1)
 
     def state_spec(self) -> StateSpec:
