@@ -116,6 +116,63 @@ def test_input_convolution_carries_its_history_in_the_slot(taps, width):
     close(out, want[:5], 1e-6, "a slot used again")
 
 
+@pytest.mark.parametrize("n,taps,width", [(1, 2, 64), (2, 3, 100), (4, 4, 2048), (3, 1, 96), (8, 8, 40), (2, None, 72)])
+def test_write_read_norm_and_convolution_in_one_pass(n, taps, width):
+    """The read that also does the write before it, and in a step of single tokens the convolution and the slots'
+    new rows too, against the separate kernels bit for bit: three requests decode for seven steps beside a padding
+    lane, their slots used out of order, a slot nobody owns full of NaN."""
+    from torchlet_b200 import ops
+
+    R, slots = 4, 5
+    dev = lambda t: t.to(DEV)
+    a, b, mix = dev(rand(n, seed=2)), dev(rand(n, seed=3)), dev(rand(n, n, seed=4))
+    w, bias = dev(1.0 + rand(width, seed=5, scale=0.3)), dev(rand(width, seed=6, scale=0.5))
+    cw = dev(rand(width, taps, seed=12, scale=0.5)) if taps else None
+    keep = (taps or 1) - 1
+    sl, req, indptr = ints([3, -1, 0, 4]), ints(range(R)), ints(range(R + 1))
+    states = []
+    for _ in range(2):
+        state = torch.full((slots, max(keep, 1), width), float("nan"), device=DEV)
+        state[[0, 3, 4]] = 0.0
+        states.append(state if keep else None)
+    z_one = dev(rand(R, n, width, seed=1, scale=2.0) + 0.5)
+    z_two = z_one.clone()
+    for step in range(7):
+        y = dev(rand(R, width, seed=20 + step))
+        # separately: write, read and norm, convolution, the slots' rows
+        side = y.clone()
+        ops.hyper_write(z_one, side, mix, b)
+        h = torch.empty(R, width, device=DEV)
+        ops.hyper_read_norm(z_one, a, w, bias, 1e-5, h)
+        want = h
+        if taps:
+            want = torch.empty(R, width, device=DEV)
+            ops.hyper_conv(h, cw, states[0], req, indptr, sl, want)
+            if keep:
+                ops.hyper_conv_state(h, states[0], indptr, sl, R)
+        # at once
+        side = y.clone()
+        got = torch.full((R, width), float("nan"), device=DEV)
+        ops.hyper_read_norm(z_two, a, w, bias, 1e-5, got, write=(side, mix, b),
+                            conv=(cw, states[1], req, sl) if taps else None)
+        assert not side.any(), "the side stream is left zeroed"
+        assert torch.equal(z_one, z_two), f"step {step}: the streams"
+        assert torch.equal(got, want), f"step {step}: what the sub-layer reads"
+        if keep:
+            assert torch.equal(states[0][[0, 3, 4]], states[1][[0, 3, 4]]), f"step {step}: the slots' rows"
+            assert torch.isnan(states[1][[1, 2]]).all(), "slots nobody owns are not touched"
+    if taps and keep:  # and against the plain convolution: request 0's seven tokens through slot 3
+        zs = rand(R, n, width, seed=1, scale=2.0) + 0.5
+        hs = []
+        zz = zs.double().permute(1, 0, 2)
+        for step in range(7):
+            zz = plain.stream_write(zz, rand(R, width, seed=20 + step).double(), mix.cpu().double(), b.cpu().double())
+            hs.append(plain.layer_norm(plain.stream_read(zz, a.cpu().double()), w.cpu().double(), bias.cpu().double(), 1e-5)[0])
+        hs = torch.stack(hs)
+        x = hs + plain.causal_conv(hs, cw.cpu().double())
+        close(got[0], x[-1], 1e-4, "the last token of request 0")
+
+
 # ------------------------------------------- attention over a window and pooled blocks
 class _Step:
     """What the bfloat16 dispatcher of the attention kernels reads of a step: ONE request that brings ``n`` tokens

@@ -8,7 +8,9 @@
 //   fanout        z[t, s] = acc[t] for every s                       (the streams start equal)
 //   collapse      acc[t] = sum_s z[t, s], ascending s
 //   read_norm     one block a token: u, then (u - mean) / sqrt(var + eps) * w + b (``centre``) or
-//                 u / sqrt(mean(u^2) + eps) * w (no centring); h float32, or T when no convolution follows
+//                 u / sqrt(mean(u^2) + eps) * w (no centring); h float32, or T when no convolution follows.
+//                 It can take the WRITE of the sub-layer before into the same pass, and, in a step of single tokens,
+//                 the convolution and the slot's new rows: a decode step then runs ONE kernel a sub-layer here
 //   conv          x[t] = h[t] + sum_j w[:, j] h[t - taps + 1 + j] over a request's tokens; rows before the step's
 //                 first token of a request come from the request's slot (the last taps - 1 rows of h that
 //                 earlier steps left; zeros at a sequence's start, which is what a cleared slot holds)
@@ -17,6 +19,8 @@
 //   write         z_t <- sum_s M[s, t] z_s + b_t y, all streams from the old ones; y is left zeroed
 //   layer_norm    rows of a float32 [tokens, width] stream (optionally gathered) -> T, with weight and bias
 #include <math.h>
+
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -52,42 +56,122 @@ __global__ void collapse_kernel(const float* __restrict__ z, float* __restrict__
 // One block a row.  ``z`` rows are [n, width] (n = 1 and a = nullptr: a plain stream); ``rows`` gathers.
 // The row is kept in shared memory between the passes; mean and variance are two block sums whose order
 // depends on the width alone.
-template <typename OutT>
-__global__ void __launch_bounds__(NORM_NT)
-read_norm_kernel(const float* __restrict__ z, const float* __restrict__ a, const float* __restrict__ weight,
-                 const float* __restrict__ bias, const int* __restrict__ rows, OutT* __restrict__ out, int n, int width,
-                 float eps, int centre) {
+//   y != nullptr: the WRITE of the sub-layer before comes first, z_t <- sum_s M[s, t] z_s + b_t y (y left zeroed),
+//                 and the read takes the new streams from registers: one pass over z instead of two.
+//   conv_w != nullptr: every request of the step brings ONE token, so a token's history is in its request's slot
+//                 alone: x = h + conv(h) is written instead of h, and the slot's rows move up by one.
+// Every sum is written as in write_kernel, conv_kernel and conv_state_kernel, so the results are theirs bit for bit.
+// The normed value, with every rounding spelt out so that all paths round alike.
+__device__ __forceinline__ float normed(float u, float mean, float inv, float w, const float* __restrict__ bias, int c) {
+  const float v = __fmul_rn(__fmul_rn(u - mean, inv), w);
+  return bias ? __fadd_rn(v, bias[c]) : v;
+}
+
+// NT threads a block: 256, or 512 for wide rows, where a thread then walks few channels (a step of few tokens is a
+// chain of dependent loads; the fewer rounds, the shorter).
+// N: the number of streams where it is 1, 2 or 4 (loops without guards, few registers), else 0 (any number up to 8).
+template <typename OutT, int NT, int N>
+__global__ void __launch_bounds__(NT)
+read_norm_kernel(float* z, const float* __restrict__ a, const float* __restrict__ weight, const float* __restrict__ bias,
+                 const int* __restrict__ rows, OutT* __restrict__ out, int n, int width, float eps, int centre,
+                 float* __restrict__ y, const float* __restrict__ mix, const float* __restrict__ b,
+                 const float* __restrict__ conv_w, float* __restrict__ conv_state, const int* __restrict__ token_req,
+                 const int* __restrict__ slots, int taps, int max_slots) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
+  constexpr int S = N > 0 ? N : MAX_STREAMS;  // the unrolled loops' bound
+  if (N > 0) n = N;
   extern __shared__ float u[];  // width
   __shared__ float scratch[32];
+  __shared__ float s_mix[MAX_STREAMS * MAX_STREAMS], s_b[MAX_STREAMS], s_a[MAX_STREAMS];
+  if (y) {
+    if (threadIdx.x < n * n) s_mix[threadIdx.x] = mix[threadIdx.x];
+    if (threadIdx.x < n) s_b[threadIdx.x] = b[threadIdx.x];
+  }
+  if (a && threadIdx.x < n) s_a[threadIdx.x] = a[threadIdx.x];
+  __syncthreads();
   const size_t src = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
-  const float* row = z + src * n * width;
+  float* row = z + src * n * width;
   float sum = 0.f;
-  for (int c = threadIdx.x; c < width; c += NORM_NT) {
-    float v;
-    if (a) {
-      v = 0.f;
-      for (int s = 0; s < n; ++s) v = fmaf(a[s], row[(size_t)s * width + c], v);
-    } else {
-      v = row[c];
+  if (y) {
+    float* add_row = y + src * width;
+    for (int c = threadIdx.x; c < width; c += NT) {
+      float old[S];
+#pragma unroll
+      for (int s = 0; s < S; ++s)
+        if (s < n) old[s] = row[(size_t)s * width + c];
+      const float add = add_row[c];
+      add_row[c] = 0.f;
+      float v = 0.f;
+#pragma unroll
+      for (int to = 0; to < S; ++to) {
+        if (to < n) {
+          float w = 0.f;
+#pragma unroll
+          for (int s = 0; s < S; ++s)
+            if (s < n) w = fmaf(s_mix[s * n + to], old[s], w);
+          w = fmaf(s_b[to], add, w);
+          row[(size_t)to * width + c] = w;
+          v = a ? fmaf(s_a[to], w, v) : w;
+        }
+      }
+      u[c] = v;
+      sum += v;
     }
-    u[c] = v;
-    sum += v;
+  } else {
+#pragma unroll 2
+    for (int c = threadIdx.x; c < width; c += NT) {
+      float v;
+      if (a) {
+        float old[S];
+#pragma unroll
+        for (int s = 0; s < S; ++s)
+          if (s < n) old[s] = row[(size_t)s * width + c];
+        v = 0.f;
+#pragma unroll
+        for (int s = 0; s < S; ++s)
+          if (s < n) v = fmaf(s_a[s], old[s], v);
+      } else {
+        v = row[c];
+      }
+      u[c] = v;
+      sum += v;
+    }
   }
   float mean = 0.f;
-  if (centre) mean = block_sum<NORM_NT>(sum, scratch) / (float)width;
+  if (centre) mean = block_sum<NT>(sum, scratch) / (float)width;
   float ss = 0.f;
-  for (int c = threadIdx.x; c < width; c += NORM_NT) {
+  for (int c = threadIdx.x; c < width; c += NT) {
     const float d = u[c] - mean;
     ss = fmaf(d, d, ss);
   }
-  const float inv = 1.f / sqrtf(block_sum<NORM_NT>(ss, scratch) / (float)width + eps);
+  const float inv = 1.f / sqrtf(block_sum<NT>(ss, scratch) / (float)width + eps);
   OutT* o = out + (size_t)blockIdx.x * width;
-  for (int c = threadIdx.x; c < width; c += NORM_NT) {
-    float v = (u[c] - mean) * inv * weight[c];
-    if (bias) v += bias[c];
-    o[c] = from_float<OutT>(v);
+  if (!conv_w) {
+#pragma unroll 2
+    for (int c = threadIdx.x; c < width; c += NT) o[c] = from_float<OutT>(normed(u[c], mean, inv, weight[c], bias, c));
+    return;
+  }
+  const int keep = taps - 1;
+  const int slot = slots[token_req[blockIdx.x]];
+  const bool live = TL_DEBUG_OK(slot >= -1 && slot < max_slots, TL_DEBUG_SLOT, slot) && slot >= 0;
+  float* mine = conv_state + (size_t)(live ? slot : 0) * keep * width;
+  for (int c = threadIdx.x; c < width; c += NT) {
+    const float v = normed(u[c], mean, inv, weight[c], bias, c);
+    float hist[MAX_TAPS];
+#pragma unroll
+    for (int r = 0; r < MAX_TAPS - 1; ++r)
+      if (r < keep) hist[r] = live ? mine[(size_t)r * width + c] : 0.f;
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS; ++j)  // ascending j: the oldest input first, the token itself last
+      if (j < taps) acc = fmaf(conv_w[(size_t)c * taps + j], j < keep ? hist[j] : v, acc);
+    o[c] = from_float<OutT>(__fadd_rn(v, acc));
+    if (live) {
+#pragma unroll
+      for (int r = 0; r < MAX_TAPS - 1; ++r)
+        if (r < keep) mine[(size_t)r * width + c] = r + 1 < keep ? hist[r + 1] : v;
+    }
   }
 }
 
@@ -142,21 +226,33 @@ __global__ void conv_state_kernel(const float* __restrict__ h, float* __restrict
   for (int r = 0; r < keep; ++r) mine[(size_t)r * width + c] = rows[r];
 }
 
-__global__ void write_kernel(float* __restrict__ z, float* __restrict__ y, const float* __restrict__ mix,
-                             const float* __restrict__ b, int n, int width, size_t total) {
+__global__ void __launch_bounds__(256)
+write_kernel(float* __restrict__ z, float* __restrict__ y, const float* __restrict__ mix, const float* __restrict__ b, int n,
+             int width, size_t total) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
+  __shared__ float s_mix[MAX_STREAMS * MAX_STREAMS], s_b[MAX_STREAMS];
+  if (threadIdx.x < n * n) s_mix[threadIdx.x] = mix[threadIdx.x];
+  if (threadIdx.x < n) s_b[threadIdx.x] = b[threadIdx.x];
+  __syncthreads();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const size_t t = i / width, c = i - t * width;
   float old[MAX_STREAMS];
-  for (int s = 0; s < n; ++s) old[s] = z[(t * n + s) * width + c];
+#pragma unroll
+  for (int s = 0; s < MAX_STREAMS; ++s)
+    if (s < n) old[s] = z[(t * n + s) * width + c];
   const float add = y[i];
   y[i] = 0.f;
-  for (int to = 0; to < n; ++to) {
-    float v = 0.f;
-    for (int s = 0; s < n; ++s) v = fmaf(mix[s * n + to], old[s], v);
-    z[(t * n + to) * width + c] = fmaf(b[to], add, v);
+#pragma unroll
+  for (int to = 0; to < MAX_STREAMS; ++to) {
+    if (to < n) {
+      float v = 0.f;
+#pragma unroll
+      for (int s = 0; s < MAX_STREAMS; ++s)
+        if (s < n) v = fmaf(s_mix[s * n + to], old[s], v);
+      z[(t * n + to) * width + c] = fmaf(s_b[to], add, v);
+    }
   }
 }
 
@@ -183,22 +279,42 @@ int tl_hyper_collapse(const float* z, float* acc, int tokens, int n, int width, 
 }
 
 // a: nullptr with n = 1 reads a plain stream; rows: nullptr or the rows to gather; bias: may be nullptr.
-int tl_hyper_read_norm(const float* z, const float* a, const float* weight, const float* bias, const int* rows, void* out,
-                       int out_dtype, int count, int n, int width, float eps, int centre, cudaStream_t stream) {
+// y, mix, b (or nullptr): the write of the sub-layer before, z_t <- sum_s mix[s, t] z_s + b_t y, in the same pass
+// (rows must be nullptr).  conv_w [width, taps] (or nullptr), conv_state [max_slots, taps - 1, width], token_req,
+// slots: the convolution of a step whose requests bring one token each; out is then h + conv(h).
+int tl_hyper_read_norm(float* z, const float* a, const float* weight, const float* bias, const int* rows, void* out,
+                       int out_dtype, int count, int n, int width, float eps, int centre, float* y, const float* mix,
+                       const float* b, const float* conv_w, float* conv_state, const int* token_req, const int* slots,
+                       int taps, int max_slots, cudaStream_t stream) {
   if (count <= 0) return 0;
   if (n <= 0 || n > MAX_STREAMS || width <= 0 || (size_t)width * sizeof(float) > 200 * 1024) return TL_ERR_UNSUPPORTED;
+  if (y && (rows || !mix || !b)) return TL_ERR_UNSUPPORTED;
+  if (conv_w && (taps < 1 || taps > MAX_TAPS || !token_req || !slots || (taps > 1 && !conv_state))) return TL_ERR_UNSUPPORTED;
   const size_t smem = (size_t)width * sizeof(float);
-  if (out_dtype == TL_DTYPE_F32) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(read_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    tl::launch_kernel(read_norm_kernel<float>, (unsigned)count, NORM_NT, smem, stream, z, a, weight, bias, rows,
-                      (float*)out, n, width, eps, centre);
-  } else {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(read_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    tl::launch_kernel(read_norm_kernel<__nv_bfloat16>, (unsigned)count, NORM_NT, smem, stream, z, a, weight, bias, rows,
-                      (__nv_bfloat16*)out, n, width, eps, centre);
+  const bool wide = width > 512;
+  auto run = [&](auto kernel, auto* typed, int threads) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    tl::launch_kernel(kernel, (unsigned)count, threads, smem, stream, z, a, weight, bias, rows, typed, n, width, eps, centre, y,
+                      mix, b, conv_w, conv_state, token_req, slots, taps, max_slots);
+  };
+  auto pick = [&](auto* typed) {
+    using OutT = std::remove_pointer_t<decltype(typed)>;
+#define TL_READ_NORM(NT)                                                         \
+  switch (n) {                                                                   \
+    case 1: run(read_norm_kernel<OutT, NT, 1>, typed, NT); break;                \
+    case 2: run(read_norm_kernel<OutT, NT, 2>, typed, NT); break;                \
+    case 4: run(read_norm_kernel<OutT, NT, 4>, typed, NT); break;                \
+    default: run(read_norm_kernel<OutT, NT, 0>, typed, NT); break;               \
   }
+    if (wide) {
+      TL_READ_NORM(512)
+    } else {
+      TL_READ_NORM(NORM_NT)
+    }
+#undef TL_READ_NORM
+  };
+  if (out_dtype == TL_DTYPE_F32) pick((float*)out);
+  else pick((__nv_bfloat16*)out);
   return TL_LAUNCH_CHECK();
 }
 

@@ -12,7 +12,8 @@
 // pooled[slot, block, kv head, d + dv] (a slot has room for the engine's longest sequence).
 //
 // Kernels:
-//   store      one block a token: its key and value rows go to its page; the token that completes a block
+//   store      one block a token copies its key and value rows to its page, one more a KV head writes the block's mean
+//              row where the token completes a block: the token that completes a block
 //              (position = b P + P - 1) also writes the block's means, summing the P rows in ascending position,
 //              rows of this step from the projection (already of type T, as the cache holds them), older ones from
 //              the pages, so the mean does not depend on how the sequence was cut into steps;
@@ -48,6 +49,8 @@ struct Layout {
   __device__ size_t value(int page, int g, int place, int page_size) const { return key(page, g, place, page_size) + v_base; }
 };
 
+// Grid (tokens, 1 + nkv): block (t, 0) copies the token's rows into its page; block (t, 1 + g) leaves at once unless
+// the token completes a block of ``pool`` tokens, and then writes the mean row of KV head g.
 template <typename T>
 __global__ void __launch_bounds__(128)
 pooled_store_kernel(const T* __restrict__ proj, int proj_stride, int k_offset, int v_offset, T* __restrict__ pages,
@@ -62,44 +65,69 @@ pooled_store_kernel(const T* __restrict__ proj, int proj_stride, int k_offset, i
   const int req = token_req[t], pos = positions[t];
   const int row = d + dv;
   const int* table = block_table + (size_t)req * table_width;
-  int page = 0;
-  if (TL_DEBUG_OK(pos / page_size < table_width, TL_DEBUG_POSITION, pos)) page = table[pos / page_size];
-  if (!TL_DEBUG_OK(page >= 0 && page < num_pages, TL_DEBUG_PAGE, page)) page = 0;
   const T* mine = proj + (size_t)t * proj_stride;
-  for (int e = threadIdx.x; e < nkv * row; e += blockDim.x) {
-    const int g = e / row, c = e - g * row;
-    if (c < d)
-      pages[at.key(page, g, pos % page_size, page_size) + c] = mine[k_offset + g * d + c];
-    else
-      pages[at.value(page, g, pos % page_size, page_size) + (c - d)] = mine[v_offset + g * dv + (c - d)];
+  if (blockIdx.y == 0) {
+    int page = 0;
+    if (TL_DEBUG_OK(pos / page_size < table_width, TL_DEBUG_POSITION, pos)) page = table[pos / page_size];
+    if (!TL_DEBUG_OK(page >= 0 && page < num_pages, TL_DEBUG_PAGE, page)) page = 0;
+    for (int e = threadIdx.x; e < nkv * row; e += blockDim.x) {
+      const int g = e / row, c = e - g * row;
+      if (c < d)
+        pages[at.key(page, g, pos % page_size, page_size) + c] = mine[k_offset + g * d + c];
+      else
+        pages[at.value(page, g, pos % page_size, page_size) + (c - d)] = mine[v_offset + g * dv + (c - d)];
+    }
+    return;
   }
   if ((pos + 1) % pool) return;
   const int slot = slots[req];
   if (!(TL_DEBUG_OK(slot >= -1 && slot < max_slots, TL_DEBUG_SLOT, slot) && slot >= 0)) return;
   const int block = pos / pool;
   if (block >= max_blocks) return;
+  const int g = blockIdx.y - 1;
   const int first = req_indptr[req];     // the request's first token of this step ...
   const int first_pos = positions[first];  // ... and its position: older rows are in the pages
-  float* out = pooled + (((size_t)slot * max_blocks + block) * nkv) * row;
+  float* out = pooled + (((size_t)slot * max_blocks + block) * nkv + g) * row;
   const float inv = 1.f / (float)pool;
-  for (int e = threadIdx.x; e < nkv * row; e += blockDim.x) {
-    const int g = e / row, c = e - g * row;
-    float sum = 0.f;
-    for (int p = pos - pool + 1; p <= pos; ++p) {
-      float v;
-      if (p >= first_pos) {
-        const T* theirs = proj + (size_t)(first + (p - first_pos)) * proj_stride;
-        v = to_float(c < d ? theirs[k_offset + g * d + c] : theirs[v_offset + g * dv + (c - d)]);
-      } else {
+  const int begin = pos - pool + 1;
+  const int old_end = first_pos < begin ? begin : (first_pos > pos + 1 ? pos + 1 : first_pos);  // [begin, old_end): in the pages
+  for (int c = threadIdx.x; c < row; c += blockDim.x) {
+    float sum = 0.f;  // ascending position, whatever the step's cut
+    int p = begin;
+    for (; p + 8 <= old_end; p += 8) {  // eight loads in flight
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
         int pg = 0;
-        if (TL_DEBUG_OK(p / page_size < table_width, TL_DEBUG_POSITION, p)) pg = table[p / page_size];
+        if (TL_DEBUG_OK((p + j) / page_size < table_width, TL_DEBUG_POSITION, p + j)) pg = table[(p + j) / page_size];
         if (!TL_DEBUG_OK(pg >= 0 && pg < num_pages, TL_DEBUG_PAGE, pg)) pg = 0;
-        v = to_float(c < d ? pages[at.key(pg, g, p % page_size, page_size) + c]
-                           : pages[at.value(pg, g, p % page_size, page_size) + (c - d)]);
+        v[j] = to_float(c < d ? pages[at.key(pg, g, (p + j) % page_size, page_size) + c]
+                              : pages[at.value(pg, g, (p + j) % page_size, page_size) + (c - d)]);
       }
-      sum += v;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sum += v[j];
     }
-    out[e] = sum * inv;
+    for (; p < old_end; ++p) {
+      int pg = 0;
+      if (TL_DEBUG_OK(p / page_size < table_width, TL_DEBUG_POSITION, p)) pg = table[p / page_size];
+      if (!TL_DEBUG_OK(pg >= 0 && pg < num_pages, TL_DEBUG_PAGE, pg)) pg = 0;
+      sum += to_float(c < d ? pages[at.key(pg, g, p % page_size, page_size) + c]
+                            : pages[at.value(pg, g, p % page_size, page_size) + (c - d)]);
+    }
+    const T* theirs = proj + (size_t)(first + (p - first_pos)) * proj_stride + (c < d ? k_offset + g * d + c : v_offset + g * dv + (c - d));
+    for (; p + 8 <= pos + 1; p += 8) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = to_float(theirs[(size_t)j * proj_stride]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sum += v[j];
+      theirs += (size_t)8 * proj_stride;
+    }
+    for (; p <= pos; ++p) {
+      sum += to_float(*theirs);
+      theirs += proj_stride;
+    }
+    out[c] = sum * inv;
   }
 }
 
@@ -225,7 +253,7 @@ pooled_prior_kernel(const T* __restrict__ q, int q_stride, const int* __restrict
                     int nkv, int d, int dv, int size, int pool, float scale_log2) {
   tl::pdl_wait();
   tl::pdl_launch_dependents();
-  __shared__ float qs[WARPS][MAX_D];
+  __shared__ __align__(16) float qs[WARPS][MAX_D];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * WARPS + warp;
   if (item >= (long long)tokens * nh) return;
@@ -260,13 +288,17 @@ pooled_prior_kernel(const T* __restrict__ q, int q_stride, const int* __restrict
       const float4* krow = reinterpret_cast<const float4*>(mine + (size_t)b * nkv * row);
       float dot = 0.f;
       if ((row & 3) == 0 && (d & 3) == 0) {
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;  // four chains instead of one of d dependent steps
+#pragma unroll 4
         for (int i = 0; i < d / 4; ++i) {
           const float4 k4 = krow[i];
-          dot = fmaf(qs[warp][4 * i], k4.x, dot);
-          dot = fmaf(qs[warp][4 * i + 1], k4.y, dot);
-          dot = fmaf(qs[warp][4 * i + 2], k4.z, dot);
-          dot = fmaf(qs[warp][4 * i + 3], k4.w, dot);
+          const float4 q4 = *reinterpret_cast<const float4*>(&qs[warp][4 * i]);
+          d0 = fmaf(q4.x, k4.x, d0);
+          d1 = fmaf(q4.y, k4.y, d1);
+          d2 = fmaf(q4.z, k4.z, d2);
+          d3 = fmaf(q4.w, k4.w, d3);
         }
+        dot = (d0 + d1) + (d2 + d3);
       } else {
         const float* k1 = mine + (size_t)b * nkv * row;
         for (int i = 0; i < d; ++i) dot = fmaf(qs[warp][i], k1[i], dot);
@@ -316,13 +348,14 @@ int tl_pooled_store(const void* proj, int proj_stride, int k_offset, int v_offse
                     const int* req_indptr, const int* slots, float* pooled, int max_blocks, int max_slots, int tokens,
                     int nkv, int d, int dv, int page_size, int pool, int num_pages, int split, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (nkv <= 0 || d <= 0 || dv <= 0 || page_size <= 0 || pool <= 0 || (split && d != dv)) return TL_ERR_UNSUPPORTED;
+  if (nkv <= 0 || nkv >= 65535 || d <= 0 || dv <= 0 || page_size <= 0 || pool <= 0 || (split && d != dv))
+    return TL_ERR_UNSUPPORTED;
   if (dtype == TL_DTYPE_F32)
-    tl::launch_kernel(pooled_store_kernel<float>, (unsigned)tokens, 128, 0, stream, (const float*)proj, proj_stride,
+    tl::launch_kernel(pooled_store_kernel<float>, dim3((unsigned)tokens, 1 + nkv), 128, 0, stream, (const float*)proj, proj_stride,
                       k_offset, v_offset, (float*)pages, block_table, table_width, token_req, positions, req_indptr,
                       slots, pooled, max_blocks, max_slots, nkv, d, dv, page_size, pool, num_pages, split);
   else
-    tl::launch_kernel(pooled_store_kernel<__nv_bfloat16>, (unsigned)tokens, 128, 0, stream,
+    tl::launch_kernel(pooled_store_kernel<__nv_bfloat16>, dim3((unsigned)tokens, 1 + nkv), 128, 0, stream,
                       (const __nv_bfloat16*)proj, proj_stride, k_offset, v_offset, (__nv_bfloat16*)pages, block_table,
                       table_width, token_req, positions, req_indptr, slots, pooled, max_blocks, max_slots, nkv, d, dv,
                       page_size, pool, num_pages, split);

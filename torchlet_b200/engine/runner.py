@@ -78,6 +78,7 @@ class StepContext:
         self.req_indptr_host = self.kv_before_host = self.slots_host = None
         self.plans: dict = {}  # per-step plans parts share across layers
         self._pending: Optional[PendingSum] = None  # see ``leave_pending``
+        self._pending_write: Optional[tuple] = None  # see ``leave_write``
         # sampling rows of the step (device), None when every sampled row is greedy
         self.num_sampled = 0
         self.sample_temperature = self.sample_seed = self.sample_counter = None
@@ -99,8 +100,27 @@ class StepContext:
         ops.workspace_holder = None
         return pending
 
+    # A block over several streams may leave the write of a sub-layer's output into them,
+    # z_t <- sum_s mix[s, t] z_s + b_t y, to the next reader of the streams, which does it in its own pass.
+    def leave_write(self, z, y, mix, b) -> None:
+        self.flush_pending()
+        self._pending_write = (z, y, mix, b)
+
+    def take_write(self, z) -> Optional[tuple]:
+        """The (y, mix, b) of the write that ``z`` still lacks, if there is one; the caller does it."""
+        pending = self._pending_write
+        if pending is None or pending[0] is not z:
+            return None
+        self._pending_write = None
+        return pending[1:]
+
     def flush_pending(self) -> None:
-        """Complete an unfinished sum into a stream (see ``leave_pending``)."""
+        """Complete an unfinished sum into a stream (see ``leave_pending``) and a write that was left
+        to the next reader (see ``leave_write``)."""
+        write = self._pending_write
+        if write is not None:
+            self._pending_write = None
+            ops.hyper_write(*write)
         pending = self._pending
         if pending is not None:
             self._pending = None

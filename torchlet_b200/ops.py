@@ -164,7 +164,8 @@ _SIGNATURES = {
         "tl_hyper_fanout": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "tl_hyper_collapse": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "tl_hyper_read_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                               c_float, c_int, c_void_p],
+                               c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                               c_int, c_void_p],
         "tl_hyper_conv": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                           c_int, c_void_p],
         "tl_hyper_conv_state": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -558,10 +559,31 @@ def hyper_collapse(z, acc) -> None:
     _check(_fn("hyper", "tl_hyper_collapse")(z.data_ptr(), acc.data_ptr(), tokens, n, width, _stream()), "hyper_collapse")
 
 
-def hyper_read_norm(z, a, weight, bias, eps: float, out, centre: bool = True, rows=None) -> None:
+def hyper_read_norm(z, a, weight, bias, eps: float, out, centre: bool = True, rows=None, write=None, conv=None) -> None:
     """out[r] = norm(sum_s a[s] z[row, s]) * weight (+ bias): a layer norm (``centre``) or an RMS norm of the streams'
-    weighted sum.  z float32 [T, n, width], or [T, width] with ``a`` None; ``rows`` (int32) gathers."""
+    weighted sum.  z float32 [T, n, width], or [T, width] with ``a`` None; ``rows`` (int32) gathers.
+    ``write`` = (y, mix, b): ``hyper_write`` of these happens first, in the same pass over z.  ``conv`` = (w, state,
+    token_req, slots) in a step whose requests bring ONE token each: out = h + conv(h) as ``hyper_conv`` gives it,
+    and the slots' rows move as ``hyper_conv_state`` moves them."""
     _need_cuda(z, a, weight, bias, out, rows)
+    y = mix = b = conv_w = conv_state = token_req = slots = None
+    taps = max_slots = 0
+    if write is not None:
+        y, mix, b = write
+        _need_cuda(y, mix, b)
+        assert rows is None and y.dtype == mix.dtype == b.dtype == torch.float32 and y.is_contiguous() and mix.is_contiguous()
+        assert y.shape == (z.shape[0], z.shape[-1]) and mix.shape == (z.shape[1], z.shape[1]) and b.numel() == z.shape[1]
+    if conv is not None:
+        conv_w, conv_state, token_req, slots = conv
+        _need_cuda(conv_w, conv_state, token_req, slots)
+        taps = conv_w.shape[1]
+        assert conv_w.dtype == torch.float32 and conv_w.is_contiguous() and conv_w.shape[0] == z.shape[-1]
+        if taps > 1:
+            assert conv_state.dtype == torch.float32 and conv_state.is_contiguous()
+            assert conv_state.shape[1:] == (taps - 1, z.shape[-1])
+            max_slots = conv_state.shape[0]
+        else:
+            conv_state = None
     n = z.shape[1] if z.dim() == 3 else 1
     width = z.shape[-1]
     count = out.shape[0]
@@ -569,7 +591,9 @@ def hyper_read_norm(z, a, weight, bias, eps: float, out, centre: bool = True, ro
     assert (a is None and n == 1) or (a is not None and a.dtype == torch.float32 and a.numel() == n)
     assert rows is not None or count == z.shape[0]
     code = _fn("hyper", "tl_hyper_read_norm")(z.data_ptr(), _ptr(a), weight.data_ptr(), _ptr(bias), _ptr(rows), out.data_ptr(),
-                                              dtype_code(out.dtype), count, n, width, float(eps), 1 if centre else 0, _stream())
+                                              dtype_code(out.dtype), count, n, width, float(eps), 1 if centre else 0,
+                                              _ptr(y), _ptr(mix), _ptr(b), _ptr(conv_w), _ptr(conv_state), _ptr(token_req),
+                                              _ptr(slots), taps, max_slots, _stream())
     _check(code, "hyper_read_norm")
 
 

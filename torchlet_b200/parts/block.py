@@ -96,7 +96,10 @@ class HyperConnectedBlock(Block):
     conv(h)_t = sum_j w[:, j] h_(t - taps + 1 + j) on each channel, zeros before a sequence's start; the last
     taps - 1 rows of h are state of the request (``cache.block_state``), so prompts may be cut anywhere.
     The read, the norm (a layer norm or an RMS norm, by the norm part's ``centre``) and the weighted sum are one
-    float32 kernel; the sub-layer adds into a zeroed float32 side stream which the write kernel leaves zeroed again.
+    float32 kernel; the sub-layer adds into a zeroed float32 side stream which the write leaves zeroed again.
+    A sub-layer's write is left to the next sub-layer's read (of this block or the next), which does both in one pass
+    over the streams (``ctx.leave_write``; whoever needs the streams earlier calls ``ctx.flush_pending``).  In a step of
+    single tokens that same kernel also convolves and moves the slots' rows: one launch a sub-layer.
 
     Parameters: ``streams`` (n), ``taps`` (None: no convolution), ``connections`` (the tensor prefixes of the two
     sub-layers' a, b, M below the layer's: ``<c>in`` [n], ``<c>out`` [n], ``<c>mix`` [n, n]), ``convolutions`` (the
@@ -168,28 +171,35 @@ class HyperConnectedBlock(Block):
 
         tokens, n, width = z.shape
         conv = self.conv[which]
-        h = ctx.buffer("hyper.h", (tokens, width), torch.float32 if conv is not None else ctx.dtype)
-        ops.hyper_read_norm(z, self.a[which], norm.weight, getattr(norm, "bias", None), norm.eps, h, centre=norm.centre)
-        x = h
-        if conv is not None:
+        write = ctx.take_write(z)  # the write of the sub-layer before, if it was left to us
+        ctx.flush_pending()
+        state = cache.block_state[which] if conv is not None and self.taps > 1 else None
+        if conv is not None and ctx.decode_only:  # a token's history is in its slot alone: one kernel
             x = ctx.buffer("hyper.x", (tokens, width), ctx.dtype)
-            state = cache.block_state[which] if self.taps > 1 else None
-            ops.hyper_conv(h, conv, state, ctx.token_req, ctx.req_indptr, ctx.slots, x)
-            if state is not None:
-                ops.hyper_conv_state(h, state, ctx.req_indptr, ctx.slots, ctx.num_requests)
+            ops.hyper_read_norm(z, self.a[which], norm.weight, getattr(norm, "bias", None), norm.eps, x, centre=norm.centre,
+                                write=write, conv=(conv, state, ctx.token_req, ctx.slots))
+        else:
+            h = ctx.buffer("hyper.h", (tokens, width), torch.float32 if conv is not None else ctx.dtype)
+            ops.hyper_read_norm(z, self.a[which], norm.weight, getattr(norm, "bias", None), norm.eps, h, centre=norm.centre,
+                                write=write)
+            x = h
+            if conv is not None:
+                x = ctx.buffer("hyper.x", (tokens, width), ctx.dtype)
+                ops.hyper_conv(h, conv, state, ctx.token_req, ctx.req_indptr, ctx.slots, x)
+                if state is not None:
+                    ops.hyper_conv_state(h, state, ctx.req_indptr, ctx.slots, ctx.num_requests)
         side = ctx.buffer("hyper.side", (tokens, width), torch.float32)
         if ctx.plans.get("hyper.side.clean") != side.data_ptr():  # the step's first sub-layer; the write kernel clears it after
             ops.fill_zero(side)
             ctx.plans["hyper.side.clean"] = side.data_ptr()
         run(x, side)
         ctx.flush_pending()
-        ops.hyper_write(z, side, self.mix[which], self.b[which])
+        ctx.leave_write(z, side, self.mix[which], self.b[which])
 
     def forward(self, ctx, acc, cache) -> None:
         if acc.dim() != 3 or acc.shape[1] != self.streams:
             raise ValueError(f"block arrangement {self.kind!r} works on [tokens, {self.streams}, width] streams "
                              "(ModelSpec.streams)")
-        ctx.flush_pending()
         self._sublayer(ctx, acc, cache, "mixer", self.norms["mixer_norm"],
                        lambda x, side: self.mixer.forward(ctx, x, side, cache))
         if self.feed_forward is not None:
