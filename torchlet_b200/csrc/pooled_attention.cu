@@ -313,7 +313,8 @@ pooled_prior_kernel(const T* __restrict__ q, int q_stride, const int* __restrict
 #pragma unroll
     for (int c = 0; c < MAX_D / 32; ++c) acc[c] *= corr;
     const int last = blocks - start < 32 ? blocks - start : 32;
-    for (int j = 0; j < last; ++j) {
+#pragma unroll 4
+    for (int j = 0; j < last; ++j) {  // four rows' loads in flight
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const float* vrow = mine + (size_t)(start + j) * nkv * row + d;
 #pragma unroll
