@@ -101,7 +101,6 @@ read_norm_kernel(float* z, const float* __restrict__ a, const float* __restrict_
       for (int s = 0; s < S; ++s)
         if (s < n) old[s] = row[(size_t)s * width + c];
       const float add = add_row[c];
-      add_row[c] = 0.f;
       float v = 0.f;
 #pragma unroll
       for (int to = 0; to < S; ++to) {
@@ -115,6 +114,9 @@ read_norm_kernel(float* z, const float* __restrict__ a, const float* __restrict_
           v = a ? fmaf(s_a[to], w, v) : w;
         }
       }
+      // cleared only now: a store issued right behind the load of the same address, while that load is still in
+      // flight, made the whole pass five times slower (measured: 146 -> 31 us for 2,048 tokens x 4 streams x 2,048)
+      add_row[c] = 0.f;
       u[c] = v;
       sum += v;
     }
@@ -243,7 +245,6 @@ write_kernel(float* __restrict__ z, float* __restrict__ y, const float* __restri
   for (int s = 0; s < MAX_STREAMS; ++s)
     if (s < n) old[s] = z[(t * n + s) * width + c];
   const float add = y[i];
-  y[i] = 0.f;
 #pragma unroll
   for (int to = 0; to < MAX_STREAMS; ++to) {
     if (to < n) {
@@ -254,6 +255,7 @@ write_kernel(float* __restrict__ z, float* __restrict__ y, const float* __restri
       z[(t * n + to) * width + c] = fmaf(s_b[to], add, v);
     }
   }
+  y[i] = 0.f;  // behind the stores that needed its old value (see read_norm_kernel)
 }
 
 }  // namespace

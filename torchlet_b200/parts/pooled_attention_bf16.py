@@ -9,6 +9,8 @@ normalize a row.  Else (False) the one-warp-a-row kernel does both.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import ops
@@ -20,9 +22,13 @@ def split_planes(head_dim: int, v_dim: int) -> bool:
     return head_dim == v_dim and head_dim in (64, 128)
 
 
+# TORCHLET_B200_POOLED_ATTENTION=plain: the one-warp-a-row kernel at every size (for measurements)
+TENSOR_CORES = os.environ.get("TORCHLET_B200_POOLED_ATTENTION", "") != "plain"
+
+
 def forward(mixer, ctx, qkv, cache, out) -> bool:
     d, nh, nkv = mixer.head_dim, mixer.num_heads, mixer.num_kv_heads
-    if cache.pages.shape[1] != 2 or not split_planes(d, mixer.v_dim) or nh // nkv > 16 or qkv.stride(0) % 8:
+    if not TENSOR_CORES or cache.pages.shape[1] != 2 or not split_planes(d, mixer.v_dim) or nh // nkv > 16 or qkv.stride(0) % 8:
         return False
     tokens = qkv.shape[0]
     ml = ctx.buffer("pooled_attention.prior_ml", (tokens, nh, 2), torch.float32)
