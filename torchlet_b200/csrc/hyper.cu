@@ -61,16 +61,33 @@ __global__ void collapse_kernel(const float* __restrict__ z, float* __restrict__
 //   conv_w != nullptr: every request of the step brings ONE token, so a token's history is in its request's slot
 //                 alone: x = h + conv(h) is written instead of h, and the slot's rows move up by one.
 // Every sum is written as in write_kernel, conv_kernel and conv_state_kernel, so the results are theirs bit for bit.
-// The normed value, with every rounding spelt out so that all paths round alike.
-__device__ __forceinline__ float normed(float u, float mean, float inv, float w, const float* __restrict__ bias, int c) {
-  const float v = __fmul_rn(__fmul_rn(u - mean, inv), w);
-  return bias ? __fadd_rn(v, bias[c]) : v;
+// V consecutive channels of a row at once (V = 4 where the width allows: 16-byte loads, and a thread of a 2,048-wide
+// row walks its channels in ONE round, which is what a step of few tokens, a chain of dependent loads, is made of).
+template <int V> __device__ __forceinline__ void load_v(const float* p, float (&out)[V]) {
+  if constexpr (V == 4) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+  } else {
+    out[0] = *p;
+  }
+}
+template <int V> __device__ __forceinline__ void store_v(float* p, const float (&v)[V]) {
+  if constexpr (V == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  else *p = v[0];
+}
+template <int V> __device__ __forceinline__ void store_v(__nv_bfloat16* p, const float (&v)[V]) {
+  if constexpr (V == 4) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const unsigned*>(&lo), *reinterpret_cast<const unsigned*>(&hi));
+  } else {
+    *p = __float2bfloat16_rn(v[0]);
+  }
 }
 
 // NT threads a block: 256, or 512 for wide rows, where a thread then walks few channels (a step of few tokens is a
 // chain of dependent loads; the fewer rounds, the shorter).
 // N: the number of streams where it is 1, 2 or 4 (loops without guards, few registers), else 0 (any number up to 8).
-template <typename OutT, int NT, int N>
+template <typename OutT, int NT, int N, int V>
 __global__ void __launch_bounds__(NT)
 read_norm_kernel(float* z, const float* __restrict__ a, const float* __restrict__ weight, const float* __restrict__ bias,
                  const int* __restrict__ rows, OutT* __restrict__ out, int n, int width, float eps, int centre,
@@ -81,7 +98,7 @@ read_norm_kernel(float* z, const float* __restrict__ a, const float* __restrict_
   tl::pdl_wait();
   constexpr int S = N > 0 ? N : MAX_STREAMS;  // the unrolled loops' bound
   if (N > 0) n = N;
-  extern __shared__ float u[];  // width
+  extern __shared__ __align__(16) float u[];  // width
   __shared__ float scratch[32];
   __shared__ float s_mix[MAX_STREAMS * MAX_STREAMS], s_b[MAX_STREAMS], s_a[MAX_STREAMS];
   if (y) {
@@ -95,84 +112,118 @@ read_norm_kernel(float* z, const float* __restrict__ a, const float* __restrict_
   float sum = 0.f;
   if (y) {
     float* add_row = y + src * width;
-    for (int c = threadIdx.x; c < width; c += NT) {
-      float old[S];
+    for (int c = threadIdx.x * V; c < width; c += NT * V) {
+      float old[S][V], add[V], v[V];
 #pragma unroll
       for (int s = 0; s < S; ++s)
-        if (s < n) old[s] = row[(size_t)s * width + c];
-      const float add = add_row[c];
-      float v = 0.f;
+        if (s < n) load_v<V>(row + (size_t)s * width + c, old[s]);
+      load_v<V>(add_row + c, add);
+#pragma unroll
+      for (int e = 0; e < V; ++e) v[e] = 0.f;
 #pragma unroll
       for (int to = 0; to < S; ++to) {
         if (to < n) {
-          float w = 0.f;
+          float w[V];
 #pragma unroll
-          for (int s = 0; s < S; ++s)
-            if (s < n) w = fmaf(s_mix[s * n + to], old[s], w);
-          w = fmaf(s_b[to], add, w);
-          row[(size_t)to * width + c] = w;
-          v = a ? fmaf(s_a[to], w, v) : w;
+          for (int e = 0; e < V; ++e) {
+            float t = 0.f;
+#pragma unroll
+            for (int s = 0; s < S; ++s)
+              if (s < n) t = fmaf(s_mix[s * n + to], old[s][e], t);
+            w[e] = fmaf(s_b[to], add[e], t);
+            v[e] = a ? fmaf(s_a[to], w[e], v[e]) : w[e];
+          }
+          store_v<V>(row + (size_t)to * width + c, w);
         }
       }
       // cleared only now: a store issued right behind the load of the same address, while that load is still in
       // flight, made the whole pass five times slower (measured: 146 -> 31 us for 2,048 tokens x 4 streams x 2,048)
-      add_row[c] = 0.f;
-      u[c] = v;
-      sum += v;
+#pragma unroll
+      for (int e = 0; e < V; ++e) add[e] = 0.f;
+      store_v<V>(add_row + c, add);
+      store_v<V>(u + c, v);
+#pragma unroll
+      for (int e = 0; e < V; ++e) sum += v[e];
     }
   } else {
-#pragma unroll 2
-    for (int c = threadIdx.x; c < width; c += NT) {
-      float v;
+    for (int c = threadIdx.x * V; c < width; c += NT * V) {
+      float v[V];
       if (a) {
-        float old[S];
+        float old[S][V];
 #pragma unroll
         for (int s = 0; s < S; ++s)
-          if (s < n) old[s] = row[(size_t)s * width + c];
-        v = 0.f;
+          if (s < n) load_v<V>(row + (size_t)s * width + c, old[s]);
 #pragma unroll
-        for (int s = 0; s < S; ++s)
-          if (s < n) v = fmaf(s_a[s], old[s], v);
+        for (int e = 0; e < V; ++e) {
+          v[e] = 0.f;
+#pragma unroll
+          for (int s = 0; s < S; ++s)
+            if (s < n) v[e] = fmaf(s_a[s], old[s][e], v[e]);
+        }
       } else {
-        v = row[c];
+        load_v<V>(row + c, v);
       }
-      u[c] = v;
-      sum += v;
+      store_v<V>(u + c, v);
+#pragma unroll
+      for (int e = 0; e < V; ++e) sum += v[e];
     }
   }
   float mean = 0.f;
   if (centre) mean = block_sum<NT>(sum, scratch) / (float)width;
   float ss = 0.f;
-  for (int c = threadIdx.x; c < width; c += NT) {
-    const float d = u[c] - mean;
-    ss = fmaf(d, d, ss);
+  for (int c = threadIdx.x * V; c < width; c += NT * V) {  // a thread reads back what it wrote itself
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      const float d = u[c + e] - mean;
+      ss = fmaf(d, d, ss);
+    }
   }
   const float inv = 1.f / sqrtf(block_sum<NT>(ss, scratch) / (float)width + eps);
   OutT* o = out + (size_t)blockIdx.x * width;
-  if (!conv_w) {
-#pragma unroll 2
-    for (int c = threadIdx.x; c < width; c += NT) o[c] = from_float<OutT>(normed(u[c], mean, inv, weight[c], bias, c));
-    return;
-  }
   const int keep = taps - 1;
-  const int slot = slots[token_req[blockIdx.x]];
-  const bool live = TL_DEBUG_OK(slot >= -1 && slot < max_slots, TL_DEBUG_SLOT, slot) && slot >= 0;
+  int slot = -1;
+  if (conv_w) slot = slots[token_req[blockIdx.x]];
+  const bool live = conv_w && TL_DEBUG_OK(slot >= -1 && slot < max_slots, TL_DEBUG_SLOT, slot) && slot >= 0;
   float* mine = conv_state + (size_t)(live ? slot : 0) * keep * width;
-  for (int c = threadIdx.x; c < width; c += NT) {
-    const float v = normed(u[c], mean, inv, weight[c], bias, c);
-    float hist[MAX_TAPS];
+  for (int c = threadIdx.x * V; c < width; c += NT * V) {
+    float w[V], bv[V], v[V];
+    load_v<V>(weight + c, w);
+    if (bias) load_v<V>(bias + c, bv);
+    float hist[MAX_TAPS - 1][V];
+    if (conv_w) {
 #pragma unroll
-    for (int r = 0; r < MAX_TAPS - 1; ++r)
-      if (r < keep) hist[r] = live ? mine[(size_t)r * width + c] : 0.f;
-    float acc = 0.f;
+      for (int r = 0; r < MAX_TAPS - 1; ++r) {
+        if (r < keep) {
+          if (live) load_v<V>(mine + (size_t)r * width + c, hist[r]);
+          else
 #pragma unroll
-    for (int j = 0; j < MAX_TAPS; ++j)  // ascending j: the oldest input first, the token itself last
-      if (j < taps) acc = fmaf(conv_w[(size_t)c * taps + j], j < keep ? hist[j] : v, acc);
-    o[c] = from_float<OutT>(__fadd_rn(v, acc));
+            for (int e = 0; e < V; ++e) hist[r][e] = 0.f;
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      v[e] = __fmul_rn(__fmul_rn(u[c + e] - mean, inv), w[e]);
+      if (bias) v[e] = __fadd_rn(v[e], bv[e]);
+    }
+    if (!conv_w) {
+      store_v<V>(o + c, v);
+      continue;
+    }
+    float x[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < MAX_TAPS; ++j)  // ascending j: the oldest input first, the token itself last
+        if (j < taps) acc = fmaf(conv_w[(size_t)(c + e) * taps + j], j < keep ? hist[j < MAX_TAPS - 1 ? j : 0][e] : v[e], acc);
+      x[e] = __fadd_rn(v[e], acc);
+    }
+    store_v<V>(o + c, x);
     if (live) {
 #pragma unroll
       for (int r = 0; r < MAX_TAPS - 1; ++r)
-        if (r < keep) mine[(size_t)r * width + c] = r + 1 < keep ? hist[r + 1] : v;
+        if (r < keep) store_v<V>(mine + (size_t)r * width + c, r + 1 < keep ? hist[r + 1 < MAX_TAPS - 1 ? r + 1 : 0] : v);
     }
   }
 }
@@ -293,7 +344,10 @@ int tl_hyper_read_norm(float* z, const float* a, const float* weight, const floa
   if (y && (rows || !mix || !b)) return TL_ERR_UNSUPPORTED;
   if (conv_w && (taps < 1 || taps > MAX_TAPS || !token_req || !slots || (taps > 1 && !conv_state))) return TL_ERR_UNSUPPORTED;
   const size_t smem = (size_t)width * sizeof(float);
-  const bool wide = width > 512;
+  // four channels a thread where rows, weights and slots' rows start on 16-byte boundaries (and the stream count has
+  // its own instance: the any-count kernel would spill)
+  const bool vec = width % 4 == 0 && (n == 1 || n == 2 || n == 4);
+  const bool wide = width / (vec ? 4 : 1) > 256;
   auto run = [&](auto kernel, auto* typed, int threads) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     tl::launch_kernel(kernel, (unsigned)count, threads, smem, stream, z, a, weight, bias, rows, typed, n, width, eps, centre, y,
@@ -301,17 +355,21 @@ int tl_hyper_read_norm(float* z, const float* a, const float* weight, const floa
   };
   auto pick = [&](auto* typed) {
     using OutT = std::remove_pointer_t<decltype(typed)>;
-#define TL_READ_NORM(NT)                                                         \
-  switch (n) {                                                                   \
-    case 1: run(read_norm_kernel<OutT, NT, 1>, typed, NT); break;                \
-    case 2: run(read_norm_kernel<OutT, NT, 2>, typed, NT); break;                \
-    case 4: run(read_norm_kernel<OutT, NT, 4>, typed, NT); break;                \
-    default: run(read_norm_kernel<OutT, NT, 0>, typed, NT); break;               \
+#define TL_READ_NORM(NT, V)                                                         \
+  switch (n) {                                                                      \
+    case 1: run(read_norm_kernel<OutT, NT, 1, V>, typed, NT); break;                \
+    case 2: run(read_norm_kernel<OutT, NT, 2, V>, typed, NT); break;                \
+    case 4: run(read_norm_kernel<OutT, NT, 4, V>, typed, NT); break;                \
+    default: run(read_norm_kernel<OutT, NT, 0, 1>, typed, NT); break;               \
   }
-    if (wide) {
-      TL_READ_NORM(512)
+    if (vec && wide) {
+      TL_READ_NORM(512, 4)
+    } else if (vec) {
+      TL_READ_NORM(NORM_NT, 4)
+    } else if (wide) {
+      TL_READ_NORM(512, 1)
     } else {
-      TL_READ_NORM(NORM_NT)
+      TL_READ_NORM(NORM_NT, 1)
     }
 #undef TL_READ_NORM
   };

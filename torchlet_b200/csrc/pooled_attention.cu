@@ -289,8 +289,8 @@ pooled_prior_kernel(const T* __restrict__ q, int q_stride, const int* __restrict
       float dot = 0.f;
       if ((row & 3) == 0 && (d & 3) == 0) {
         float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;  // four chains instead of one of d dependent steps
-#pragma unroll 4
-        for (int i = 0; i < d / 4; ++i) {
+#pragma unroll 16
+        for (int i = 0; i < d / 4; ++i) {  // sixteen loads of the lane's own row in flight
           const float4 k4 = krow[i];
           const float4 q4 = *reinterpret_cast<const float4*>(&qs[warp][4 * i]);
           d0 = fmaf(q4.x, k4.x, d0);
@@ -313,8 +313,8 @@ pooled_prior_kernel(const T* __restrict__ q, int q_stride, const int* __restrict
 #pragma unroll
     for (int c = 0; c < MAX_D / 32; ++c) acc[c] *= corr;
     const int last = blocks - start < 32 ? blocks - start : 32;
-#pragma unroll 4
-    for (int j = 0; j < last; ++j) {  // four rows' loads in flight
+#pragma unroll 8
+    for (int j = 0; j < last; ++j) {  // eight rows' loads in flight
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const float* vrow = mine + (size_t)(start + j) * nkv * row + d;
 #pragma unroll
