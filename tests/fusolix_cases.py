@@ -61,7 +61,8 @@ CASES = {
                     moe(3, 3, 24, 3, 3), 1.0, 0.8),
               layer(left(3, 1, 20, 12, 0.2, 30, 30), right(2, 20, 12, (0.97, 0.99), 20, 100.0), dense(72, 0.7), 0.9, 1.0),
           ]},
-    # head sizes of 64 and 128 (what tensor-core kernels take), windows and blocks over several pages, five taps
+    # head sizes of 64 and 128 (equal key and value sizes of these run on the tensor-core kernels: the first and the
+    # last layer), windows and blocks over several pages, five taps
     "R": {"architecture": "Fusolix", "vocab": 211, "width": 128, "streams": 4, "norm": {"eps": 1e-6},
           "embedding": {"scale": 0.25}, "canon": {"taps": 5},
           "layers": [
@@ -70,6 +71,7 @@ CASES = {
               layer(left(6, 2, 128, 64, 0.09, 70, 24), right(1, 128, 32, (0.98,), 64, 50000.0), dense(192, 2.5), 1.1, 0.9),
               layer(left(2, 2, 64, 128, 0.125, 33, 8), right(4, 32, 64, (0.9, 0.95, 0.99, 0.999), 32, 50000.0),
                     moe(4, 2, 64, 2, 1), 0.8, 0.8),
+              layer(left(8, 2, 128, 128, 0.09, 40, 8), right(2, 32, 32, (0.95, 0.99), 16, 50000.0), None, 0.9, 1.2),
           ]},
     # ONE tap (the convolution is a factor on the token itself and keeps nothing), two streams, one expert of two groups
     "S": {"architecture": "Fusolix", "vocab": 53, "width": 48, "streams": 2, "norm": {"eps": 1e-5},

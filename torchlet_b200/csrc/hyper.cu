@@ -88,7 +88,7 @@ template <int V> __device__ __forceinline__ void store_v(__nv_bfloat16* p, const
 // chain of dependent loads; the fewer rounds, the shorter).
 // N: the number of streams where it is 1, 2 or 4 (loops without guards, few registers), else 0 (any number up to 8).
 template <typename OutT, int NT, int N, int V>
-__global__ void __launch_bounds__(NT)
+__global__ void __launch_bounds__(NT, N > 0 ? 1024 / NT : 1)  // 64 registers: 1,024 threads an SM and more (48 % -> of the DRAM peak)
 read_norm_kernel(float* z, const float* __restrict__ a, const float* __restrict__ weight, const float* __restrict__ bias,
                  const int* __restrict__ rows, OutT* __restrict__ out, int n, int width, float eps, int centre,
                  float* __restrict__ y, const float* __restrict__ mix, const float* __restrict__ b,
