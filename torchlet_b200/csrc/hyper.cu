@@ -106,18 +106,25 @@ read_norm_kernel(float* z, const float* __restrict__ a, const float* __restrict_
     if (threadIdx.x < n) s_b[threadIdx.x] = b[threadIdx.x];
   }
   if (a && threadIdx.x < n) s_a[threadIdx.x] = a[threadIdx.x];
-  __syncthreads();
   const size_t src = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
   float* row = z + src * n * width;
   float sum = 0.f;
   if (y) {
     float* add_row = y + src * width;
-    for (int c = threadIdx.x * V; c < width; c += NT * V) {
-      float old[S][V], add[V], v[V];
+    // A round's loads are asked for one round ahead, the first ones before the coefficients have arrived: in a step
+    // of few tokens the kernel is a chain of dependent trips to memory, and this takes one out.
+    float old[S][V], add[V];
+    int c = threadIdx.x * V;
+    auto fetch = [&](int at) {
 #pragma unroll
       for (int s = 0; s < S; ++s)
-        if (s < n) load_v<V>(row + (size_t)s * width + c, old[s]);
-      load_v<V>(add_row + c, add);
+        if (s < n) load_v<V>(row + (size_t)s * width + at, old[s]);
+      load_v<V>(add_row + at, add);
+    };
+    if (c < width) fetch(c);
+    __syncthreads();
+    while (c < width) {
+      float v[V];
 #pragma unroll
       for (int e = 0; e < V; ++e) v[e] = 0.f;
 #pragma unroll
@@ -138,14 +145,18 @@ read_norm_kernel(float* z, const float* __restrict__ a, const float* __restrict_
       }
       // cleared only now: a store issued right behind the load of the same address, while that load is still in
       // flight, made the whole pass five times slower (measured: 146 -> 31 us for 2,048 tokens x 4 streams x 2,048)
+      float zero[V];
 #pragma unroll
-      for (int e = 0; e < V; ++e) add[e] = 0.f;
-      store_v<V>(add_row + c, add);
+      for (int e = 0; e < V; ++e) zero[e] = 0.f;
+      store_v<V>(add_row + c, zero);
       store_v<V>(u + c, v);
 #pragma unroll
       for (int e = 0; e < V; ++e) sum += v[e];
+      c += NT * V;
+      if (c < width) fetch(c);
     }
   } else {
+    __syncthreads();
     for (int c = threadIdx.x * V; c < width; c += NT * V) {
       float v[V];
       if (a) {
