@@ -33,8 +33,8 @@ __global__ void fill_zero_scalar_kernel(float* __restrict__ p, size_t n) {
   if (i < n) p[i] = 0.f;
 }
 
-__global__ void scaled_add_scalar_kernel(float* __restrict__ acc, const float* __restrict__ delta, float m,
-                                         __nv_bfloat16* __restrict__ cast, size_t n) {
+__global__ void scaled_add_scalar_kernel(float* __restrict__ acc, float* __restrict__ delta, float m,
+                                         __nv_bfloat16* __restrict__ cast, size_t n, int clear) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -42,6 +42,7 @@ __global__ void scaled_add_scalar_kernel(float* __restrict__ acc, const float* _
   const float a = fmaf(m, delta[i], acc[i]);
   acc[i] = a;
   if (cast) cast[i] = __float2bfloat16_rn(a);
+  if (clear) delta[i] = 0.f;  // behind the store that needed its old value
 }
 
 __global__ void scale_kernel(float* __restrict__ p, float alpha, size_t n) {
@@ -51,9 +52,10 @@ __global__ void scale_kernel(float* __restrict__ p, float alpha, size_t n) {
   if (i < n) p[i] *= alpha;
 }
 
-// acc += m * delta over float4; cast (optional) receives the updated stream in bfloat16.
-__global__ void scaled_add_kernel(float4* __restrict__ acc, const float4* __restrict__ delta, float m,
-                                  uint2* __restrict__ cast, size_t quads) {
+// acc += m * delta over float4; cast (optional) receives the updated stream in bfloat16; clear: delta is left zeroed
+// (for the next branch to add into).
+__global__ void scaled_add_kernel(float4* __restrict__ acc, float4* __restrict__ delta, float m,
+                                  uint2* __restrict__ cast, size_t quads, int clear) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -69,6 +71,7 @@ __global__ void scaled_add_kernel(float4* __restrict__ acc, const float4* __rest
     __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
     cast[i] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
   }
+  if (clear) delta[i] = make_float4(0.f, 0.f, 0.f, 0.f);  // behind the store that needed its old value
 }
 
 // One block per row: acc[r] += m * y[r] * rsqrt(mean(y[r]^2) + eps) * w.  The order of the
@@ -206,17 +209,17 @@ int tl_scale(float* p, float alpha, long long n, cudaStream_t stream) {
   return TL_LAUNCH_CHECK();
 }
 
-int tl_scaled_add(float* acc, const float* delta, float m, void* cast, long long n, cudaStream_t stream) {
+int tl_scaled_add(float* acc, float* delta, float m, void* cast, long long n, int clear, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (n % 4 || ((reinterpret_cast<uintptr_t>(acc) | reinterpret_cast<uintptr_t>(delta)) & 15) ||
       (reinterpret_cast<uintptr_t>(cast) & 7)) {
     tl::launch_kernel(scaled_add_scalar_kernel, (unsigned)(((size_t)n + 255) / 256), 256, 0, stream, acc, delta, m,
-                      (__nv_bfloat16*)cast, (size_t)n);
+                      (__nv_bfloat16*)cast, (size_t)n, clear);
     return TL_LAUNCH_CHECK();
   }
   const size_t quads = (size_t)n / 4;
   tl::launch_kernel(scaled_add_kernel, (unsigned)((quads + 255) / 256), 256, 0, stream, (float4*)acc,
-                    (const float4*)delta, m, (uint2*)cast, quads);
+                    (float4*)delta, m, (uint2*)cast, quads, clear);
   return TL_LAUNCH_CHECK();
 }
 

@@ -100,7 +100,7 @@ _SIGNATURES = {
     "stream_ops": {
         "tl_fill_zero": [c_void_p, c_longlong, c_void_p],
         "tl_scale": [c_void_p, c_float, c_longlong, c_void_p],
-        "tl_scaled_add": [c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_void_p],
+        "tl_scaled_add": [c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_int, c_void_p],
         "tl_rms_scaled_add": [c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int, c_void_p],
         "tl_rms_scaled_add_partials": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_float, c_float, c_int, c_int, c_int,
                                        c_void_p],
@@ -364,14 +364,16 @@ def scale_(x: torch.Tensor, alpha: float) -> None:
     _check(_fn("stream_ops", "tl_scale")(x.data_ptr(), float(alpha), x.numel(), _stream()), "scale")
 
 
-def scaled_add(acc: torch.Tensor, delta: torch.Tensor, m: float, cast: torch.Tensor | None = None) -> None:
-    """acc += m * delta (float32); ``cast`` (bfloat16, same shape) also receives the updated acc."""
+def scaled_add(acc: torch.Tensor, delta: torch.Tensor, m: float, cast: torch.Tensor | None = None,
+               clear: bool = False) -> None:
+    """acc += m * delta (float32); ``cast`` (bfloat16, same shape) also receives the updated acc; ``clear``: delta is
+    left zeroed."""
     _need_cuda(acc, delta, cast)
     assert acc.dtype == delta.dtype == torch.float32 and acc.shape == delta.shape
     assert acc.is_contiguous() and delta.is_contiguous()
     assert cast is None or (cast.dtype == torch.bfloat16 and cast.shape == acc.shape and cast.is_contiguous())
     code = _fn("stream_ops", "tl_scaled_add")(acc.data_ptr(), delta.data_ptr(), float(m), _ptr(cast), acc.numel(),
-                                              _stream())
+                                              1 if clear else 0, _stream())
     _check(code, "scaled_add")
 
 

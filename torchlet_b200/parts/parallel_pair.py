@@ -61,7 +61,9 @@ class ParallelMixers(Mixer):
                 part.forward(ctx, x, acc, mine)
                 continue
             side = ctx.buffer("parallel_mixers.side", tuple(acc.shape), torch.float32)
-            ops.fill_zero(side)
+            if ctx.plans.get("parallel_mixers.side.clean") != side.data_ptr():  # the step's first scaled branch
+                ops.fill_zero(side)
+                ctx.plans["parallel_mixers.side.clean"] = side.data_ptr()
             part.forward(ctx, x, side, mine)
             ctx.flush_pending()
-            ops.scaled_add(acc, side, scale)
+            ops.scaled_add(acc, side, scale, clear=True)  # zeroed again for the next branch to add into
