@@ -88,8 +88,16 @@ class CacheStorage:
     def state_tensors(self) -> list:
         """Every state tensor (of mixers and of block arrangements), flat."""
         out = []
+
+        def walk(held) -> None:
+            if isinstance(held, dict):  # several states of one part, or of the branches of a part
+                for one in held.values():
+                    walk(one)
+            elif held is not None:
+                out.append(held)
+
         for held in (*self.states.values(), *self.block_states.values()):
-            out += list(held.values()) if isinstance(held, dict) else [held]
+            walk(held)
         return out
 
     def bytes(self) -> int:

@@ -12,11 +12,13 @@ from .qwen2 import Qwen2Config
 from .dodonex import DodonexConfig
 from .numuzen import NumuzenConfig
 from .fusolix import FusolixConfig
+from .kilatar import KilatarConfig
 
 __all__ = [
     "DodonexConfig",
     "EngineConfig",
     "FusolixConfig",
+    "KilatarConfig",
     "LayerSpec",
     "ModelSpec",
     "NumuzenConfig",

@@ -74,11 +74,15 @@ class ScheduleEntry:
 
     ``layer`` indexes ``ModelSpec.layers`` and may appear more than once in the
     schedule.  Each entry owns the cache of its execution unless ``cache_from``
-    names an earlier entry, whose cache it then reads without writing.
+    names an earlier entry, whose cache it then reads without writing.  ``add_embedding``: before this
+    execution the embedding output (the stream as it entered the first layer) is added to the stream
+    (a model that runs a stretch of its layers several times feeds its input in again before each
+    further pass).
     """
 
     layer: int
     cache_from: Optional[int] = None
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)
@@ -99,12 +103,17 @@ class ModelSpec:
     # None: one residual stream [T, hidden].  n >= 1: the blocks work on n streams a token, [T, n, hidden], which all
     # start as the embedding output and are summed before the final norm (every block must be of such a kind).
     streams: Optional[int] = None
+    # a norm of the embedding rows (after the scale) before the first layer; its tensors lie below the prefix
+    embedding_norm: Optional[PartSpec] = None
+    embedding_norm_prefix: str = "embedding_norm."
 
     def validate(self) -> None:
         if not self.layers:
             raise ValueError("a model needs at least one layer")
         if not self.schedule:
             raise ValueError("the layer schedule is empty")
+        if self.streams is not None and any(entry.add_embedding for entry in self.schedule):
+            raise ValueError("adding the embedding output again is not built for several residual streams")
         for i, entry in enumerate(self.schedule):
             if not 0 <= entry.layer < len(self.layers):
                 raise ValueError(

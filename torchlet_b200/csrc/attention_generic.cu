@@ -47,7 +47,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
   const int t = (int)(item / nh), h = (int)(item % nh);
   const int kvh = h / (nh / nkv);
   const int pos = positions[t];
-  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int lo = first_key(pos, window);
   const int* table = block_table + (size_t)token_req[t] * table_width;
 
   const T* qrow = q + (size_t)t * q_stride + (size_t)h * d;

@@ -287,8 +287,7 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
   }
   const int first_tok = row_start / g, last_tok = (row_end - 1) / g;
   const int hi_key = before + last_tok;  // last key any row of the tile may see
-  int lo_key = 0;
-  if (p.window > 0) lo_key = max(0, before + first_tok - p.window + 1);
+  const int lo_key = tl::first_key(before + first_tok, p.window);
 
   // key tiles of this CTA
   int tile_begin = lo_key / BLOCK_N, tile_end = hi_key / BLOCK_N + 1;
@@ -363,7 +362,7 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
     const int row = row_start + my_rows + (lane >> 2) + 8 * h;
     if (row < row_end) {
       row_pos[h] = before + row / g;
-      row_lo[h] = p.window > 0 ? max(0, row_pos[h] - p.window + 1) : 0;
+      row_lo[h] = tl::first_key(row_pos[h], p.window);
     } else {
       row_pos[h] = -1;  // sees no key
       row_lo[h] = 0;
@@ -708,7 +707,7 @@ attention_combine_kernel(const float* __restrict__ part_acc, const float* __rest
   const int req = tile_req ? tile_req[tile] : tile;
   // the splits this request used: as the attention kernel counted them
   const int hi_key = kv_before[req];
-  const int lo_key = window > 0 ? max(0, hi_key - window + 1) : 0;
+  const int lo_key = tl::first_key(hi_key, window);
   const int splits = effective_splits(grid_splits, hi_key / BLOCK_N + 1 - lo_key / BLOCK_N);
   const float* ml = part_ml + (size_t)item * grid_splits * 2;
   if (c < 32) {  // splits <= 64: two per lane

@@ -220,7 +220,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
     t.begin = t.end = 0;
     if (t.row_start < t.row_end) {
       const int first_tok = t.row_start / g, last_tok = (t.row_end - 1) / g;
-      const int lo_key = p.window > 0 ? max(0, before + first_tok - p.window + 1) : 0;
+      const int lo_key = tl::first_key(before + first_tok, p.window);
       t.begin = lo_key / KEYS;
       t.end = (before + last_tok) / KEYS + 1;
       if (x == 0) cta_lo_key = lo_key;
@@ -402,7 +402,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
     const int row = mine.row_start + r;
     const bool row_valid = r < p.rows_per_tile && row < mine.row_end;
     const int pos = row_valid ? before + row / g : -1;
-    const int lo = (row_valid && p.window > 0) ? max(0, pos - p.window + 1) : 0;
+    const int lo = row_valid ? tl::first_key(pos, p.window) : 0;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const uint32_t tmem_s = tmem_base + x * KEYS + lane_base;
     const uint32_t tmem_o = tmem_base + 256 + x * D + lane_base;

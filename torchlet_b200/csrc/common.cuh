@@ -115,6 +115,16 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
   return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
 }
 
+// The first key position a query at position ``pos`` sees, by the mask code all paged attention kernels share:
+// window > 0: the last ``window`` positions, the query's own included; window < 0: the positions of the query's own
+// chunk of -window positions (chunks are counted from position 0 of the sequence); 0: every position before it.
+// Monotone in ``pos`` in all three forms, so a tile's first key is that of its first row.
+__device__ __forceinline__ int first_key(int pos, int window) {
+  if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+  if (window < 0) return pos > 0 ? pos - pos % (-window) : 0;
+  return 0;
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -90,25 +90,31 @@ constexpr int KS = 4;
 constexpr int COLS = 32;
 constexpr int STAGES = 4;
 
-// FIXED: the decay is one constant per head (``decay`` holds ``heads`` numbers; a retention), not a row per token.
-template <int DK, bool VEC, bool FIXED>
+// MODE says what ``decay`` holds: DECAY_ROWS a row [heads * dim] per token (one number a key channel), DECAY_HEAD one
+// constant per head (``heads`` numbers; a retention), DECAY_TOKEN one number per (token, head) for all of the head's
+// key channels (a selective state space).  ``qk_heads``: q and k have that many heads (a divisor of ``heads``), head h
+// reading q/k head h / (heads / qk_heads); the rows are [ q (qk_heads D) | k (qk_heads D) | v (heads V) | ... ].
+constexpr int DECAY_ROWS = 0, DECAY_HEAD = 1, DECAY_TOKEN = 2;
+template <int DK, bool VEC, int MODE>
 __global__ void __launch_bounds__(KS * COLS)
 gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ decay,
                 const int* __restrict__ req_indptr, const int* __restrict__ slots, float* __restrict__ state,
-                float* __restrict__ out, int heads, int dim, int vdim, int max_slots, float qscale) {
+                float* __restrict__ out, int heads, int qk_heads, int dim, int vdim, int max_slots, float qscale) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
+  constexpr bool FIXED = MODE != DECAY_ROWS;  // no decay row is staged
   constexpr int PER = DK / KS;
   constexpr int CHUNK = DK <= 64 ? 8 : (DK <= 128 ? 4 : 2);
-  __shared__ __align__(16) float stage[STAGES * CHUNK * (3 * DK + COLS)];  // [STAGES][CHUNK]: q, k, a, v
-  constexpr int row = 3 * DK + COLS;
+  __shared__ __align__(16) float stage[STAGES * CHUNK * (3 * DK + COLS + 4)];  // [STAGES][CHUNK]: q, k, a, v, token's decay
+  constexpr int row = 3 * DK + COLS + 4;
   constexpr int NT = KS * COLS;
   const int req = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
   const int col0 = blockIdx.z * COLS;  // this block's value channels: col0 .. col0 + COLS
   const int cols_here = vdim - col0 < COLS ? vdim - col0 : COLS;
   const int part = tid % KS, col = col0 + tid / KS;
   const bool on = col < vdim;
-  const int hd = heads * dim, hv = heads * vdim;
+  const int hd = qk_heads * dim, hv = heads * vdim;
+  const int hq = h / (heads / qk_heads);  // the q/k head this head reads
   const int first = req_indptr[req], last = req_indptr[req + 1];
   const int slot = slots[req];
   const bool live = TL_DEBUG_OK(slot >= -1 && slot < max_slots, TL_DEBUG_SLOT, slot) && slot >= 0;
@@ -124,7 +130,7 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
     const int count = last - base < CHUNK ? last - base : CHUNK;
     float* dst = stage + (size_t)buf * CHUNK * row;
     if (VEC) {
-      const int qd = dim >> 2, qv = cols_here >> 2, per_token = (FIXED ? 2 : 3) * qd + qv;
+      const int qd = dim >> 2, qv = cols_here >> 2, per_token = (FIXED ? 2 : 3) * qd + qv + (MODE == DECAY_TOKEN ? 1 : 0);
       for (int e = tid; e < count * per_token; e += NT) {
         const int tt = e / per_token, rest = e - tt * per_token;
         const int t = base + tt;
@@ -132,12 +138,15 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
         float* to;
         if (rest < 2 * qd) {  // q, k
           const int what = rest / qd, q4 = rest - what * qd;
-          src = proj + (size_t)t * proj_stride + what * hd + h * dim + 4 * q4;
+          src = proj + (size_t)t * proj_stride + what * hd + hq * dim + 4 * q4;
           to = dst + tt * row + what * DK + 4 * q4;
         } else if (!FIXED && rest < 3 * qd) {
           const int q4 = rest - 2 * qd;
-          src = decay + (size_t)t * hd + h * dim + 4 * q4;
+          src = decay + (size_t)t * heads * dim + h * dim + 4 * q4;
           to = dst + tt * row + 2 * DK + 4 * q4;
+        } else if (MODE == DECAY_TOKEN && rest == per_token - 1) {
+          copy4(dst + tt * row + 3 * DK + COLS, decay + (size_t)t * heads + h);
+          continue;
         } else {
           const int q4 = rest - (FIXED ? 2 : 3) * qd;
           src = proj + (size_t)t * proj_stride + 2 * hd + h * vdim + col0 + 4 * q4;
@@ -146,7 +155,7 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
         copy16(to, src);
       }
     } else {
-      const int per_token = (FIXED ? 2 : 3) * dim + cols_here;
+      const int per_token = (FIXED ? 2 : 3) * dim + cols_here + (MODE == DECAY_TOKEN ? 1 : 0);
       for (int e = tid; e < count * per_token; e += NT) {
         const int tt = e / per_token, rest = e - tt * per_token;
         const int t = base + tt;
@@ -154,12 +163,15 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
         float* to;
         if (rest < 2 * dim) {
           const int what = rest / dim, i = rest - what * dim;
-          src = proj + (size_t)t * proj_stride + what * hd + h * dim + i;
+          src = proj + (size_t)t * proj_stride + what * hd + hq * dim + i;
           to = dst + tt * row + what * DK + i;
         } else if (!FIXED && rest < 3 * dim) {
           const int i = rest - 2 * dim;
-          src = decay + (size_t)t * hd + h * dim + i;
+          src = decay + (size_t)t * heads * dim + h * dim + i;
           to = dst + tt * row + 2 * DK + i;
+        } else if (MODE == DECAY_TOKEN && rest == per_token - 1) {
+          src = decay + (size_t)t * heads + h;
+          to = dst + tt * row + 3 * DK + COLS;
         } else {
           const int i = rest - (FIXED ? 2 : 3) * dim;
           src = proj + (size_t)t * proj_stride + 2 * hd + h * vdim + col0 + i;
@@ -184,7 +196,7 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
     S[n] = (on && i < dim) ? mine[(size_t)i * vdim + col] : 0.f;
   }
 
-  const float fixed = FIXED ? decay[h] : 0.f;
+  const float head_decay = MODE == DECAY_HEAD ? decay[h] : 0.f;
   int buf = 0;
   for (int base = first; base < last; base += CHUNK, buf = (buf + 1) % STAGES) {
     const int count = last - base < CHUNK ? last - base : CHUNK;
@@ -200,6 +212,7 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
       const float4* k4 = reinterpret_cast<const float4*>(tok + DK);
       const float4* a4 = reinterpret_cast<const float4*>(tok + 2 * DK);
       const float v = tok[3 * DK + (on ? col - col0 : 0)];
+      const float fixed = MODE == DECAY_TOKEN ? tok[3 * DK + COLS] : head_decay;
       float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
       for (int n = 0; n < PER / 4; ++n) {
@@ -296,26 +309,31 @@ int tl_gla_decay(const float* proj, int proj_stride, int low_offset, const float
 }
 
 // state: float32 [max_slots, heads, dim, vdim]; out: float32 [tokens, heads * vdim].
-// fixed_decay: ``decay`` holds one constant per head instead of [tokens, heads * dim] rows.
+// decay_mode: 0 ``decay`` holds [tokens, heads * dim] rows, 1 one constant per head, 2 [tokens, heads] (one number per
+// token and head).  qk_heads: how many heads q and k have (divides heads).
 int tl_gla_scan(const float* proj, int proj_stride, const float* decay, const int* req_indptr, const int* slots,
-                float* state, float* out, int requests, int heads, int dim, int vdim, int max_slots, float qscale,
-                int fixed_decay, cudaStream_t stream) {
+                float* state, float* out, int requests, int heads, int qk_heads, int dim, int vdim, int max_slots,
+                float qscale, int decay_mode, cudaStream_t stream) {
   if (requests <= 0) return 0;
   if (dim <= 0 || dim > 256 || vdim <= 0 || vdim > 256 || heads > 65535) return TL_ERR_UNSUPPORTED;
+  if (qk_heads <= 0 || heads % qk_heads || decay_mode < 0 || decay_mode > 2) return TL_ERR_UNSUPPORTED;
+  const bool fixed_decay = decay_mode != DECAY_ROWS;
   dim3 grid(requests, heads, (vdim + COLS - 1) / COLS);
   const int threads = KS * COLS;
-  const bool vec = dim % 4 == 0 && vdim % 4 == 0 && proj_stride % 4 == 0 && (heads * dim) % 4 == 0 &&
+  const bool vec = dim % 4 == 0 && vdim % 4 == 0 && proj_stride % 4 == 0 && (qk_heads * dim) % 4 == 0 &&
                    (reinterpret_cast<uintptr_t>(proj) & 15) == 0 &&
                    (fixed_decay || (reinterpret_cast<uintptr_t>(decay) & 15) == 0);
-#define TL_SCAN_ONE(DK, VEC, FIXED)                                                                                 \
-  tl::launch_kernel(gla_scan_kernel<DK, VEC, FIXED>, grid, threads, 0, stream, proj, proj_stride, decay, req_indptr, \
-                    slots, state, out, heads, dim, vdim, max_slots, qscale)
-#define TL_SCAN(DK)                                                  \
-  {                                                                  \
-    if (vec && fixed_decay) TL_SCAN_ONE(DK, true, true);             \
-    else if (vec) TL_SCAN_ONE(DK, true, false);                      \
-    else if (fixed_decay) TL_SCAN_ONE(DK, false, true);              \
-    else TL_SCAN_ONE(DK, false, false);                              \
+#define TL_SCAN_ONE(DK, VEC, MODE)                                                                                 \
+  tl::launch_kernel(gla_scan_kernel<DK, VEC, MODE>, grid, threads, 0, stream, proj, proj_stride, decay, req_indptr, \
+                    slots, state, out, heads, qk_heads, dim, vdim, max_slots, qscale)
+#define TL_SCAN(DK)                                                                \
+  {                                                                                \
+    if (vec && decay_mode == DECAY_HEAD) TL_SCAN_ONE(DK, true, DECAY_HEAD);        \
+    else if (vec && decay_mode == DECAY_TOKEN) TL_SCAN_ONE(DK, true, DECAY_TOKEN); \
+    else if (vec) TL_SCAN_ONE(DK, true, DECAY_ROWS);                               \
+    else if (decay_mode == DECAY_HEAD) TL_SCAN_ONE(DK, false, DECAY_HEAD);         \
+    else if (decay_mode == DECAY_TOKEN) TL_SCAN_ONE(DK, false, DECAY_TOKEN);       \
+    else TL_SCAN_ONE(DK, false, DECAY_ROWS);                                       \
   }
   if (dim <= 16) TL_SCAN(16)
   else if (dim <= 32) TL_SCAN(32)

@@ -42,7 +42,7 @@ latent_prepare_kernel(const float* __restrict__ down, int down_stride, int q_ran
   __shared__ float scratch[32];
   const int t = blockIdx.x;
   const float* row = down + (size_t)t * down_stride;
-  {
+  if (q_rank > 0) {  // 0: the queries come straight from the layer's input, there is no query latent
     float ss = 0.f;
     for (int i = threadIdx.x; i < q_rank; i += NT) ss = fmaf(row[i], row[i], ss);
     ss = block_sum<NT>(ss, scratch);

@@ -49,9 +49,13 @@ __device__ __forceinline__ float router_logit(const Row* __restrict__ row, const
 // their weights.
 // ``groups`` > 1 with ``keep`` < groups: the experts form ``groups`` equal groups of neighbours, a group is scored by
 // its largest member, and only experts of the ``keep`` best groups (the lower index wins a tie) can be chosen.
-__device__ __forceinline__ void choose_experts(float* score, int experts, int top, int softmax_scores, int renormalize,
+// ``pick`` (shared memory, ``experts`` floats; may be ``score`` itself): the numbers the choice goes by.  With a
+// ``correction`` (one number an expert) they are score + correction, while the weights stay the scores.  The weights
+// are multiplied by ``scale`` at the end.
+__device__ __forceinline__ void choose_experts(float* score, float* pick, const float* __restrict__ correction,
+                                               int experts, int top, int softmax_scores, int renormalize,
                                                int lane, int* __restrict__ choice, float* __restrict__ weight,
-                                               int groups, int keep, float renorm_eps) {
+                                               int groups, int keep, float renorm_eps, float scale) {
   if (softmax_scores) {
     float m = -INFINITY;
     for (int e = lane; e < experts; e += 32) m = fmaxf(m, score[e]);
@@ -64,6 +68,9 @@ __device__ __forceinline__ void choose_experts(float* score, int experts, int to
     for (int e = lane; e < experts; e += 32) score[e] = 1.f / (1.f + expf(-score[e]));
   }
   __syncwarp();
+  if (pick != score)
+    for (int e = lane; e < experts; e += 32) pick[e] = score[e] + correction[e];
+  __syncwarp();
   if (groups > 1 && keep < groups) {
     const int per = experts / groups;
     // lane g (and g + 32, ...) holds group g's score; ``kept`` groups are marked by a bit per group and lane
@@ -74,7 +81,7 @@ __device__ __forceinline__ void choose_experts(float* score, int experts, int to
       for (int g = lane, i = 0; g < groups; g += 32, ++i) {
         if (mine >> i & 1ull) continue;
         float top_of = -INFINITY;
-        for (int e = g * per; e < (g + 1) * per; ++e) top_of = fmaxf(top_of, score[e]);
+        for (int e = g * per; e < (g + 1) * per; ++e) top_of = fmaxf(top_of, pick[e]);
         if (top_of > best) { best = top_of; at = g; }
       }
 #pragma unroll
@@ -87,7 +94,7 @@ __device__ __forceinline__ void choose_experts(float* score, int experts, int to
     }
     for (int g = lane, i = 0; g < groups; g += 32, ++i)
       if (!(mine >> i & 1ull))
-        for (int e = g * per; e < (g + 1) * per; ++e) score[e] = -INFINITY;
+        for (int e = g * per; e < (g + 1) * per; ++e) pick[e] = -INFINITY;
     __syncwarp();
   }
   float total = 0.f;
@@ -95,7 +102,7 @@ __device__ __forceinline__ void choose_experts(float* score, int experts, int to
     float best = -INFINITY;
     int at = experts;
     for (int e = lane; e < experts; e += 32) {
-      const float s = score[e];
+      const float s = pick[e];
       if (s > best) { best = s; at = e; }  // ascending e: the lower index keeps a tie
     }
 #pragma unroll
@@ -105,16 +112,18 @@ __device__ __forceinline__ void choose_experts(float* score, int experts, int to
       if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
     }
     if (at >= experts) at = 0;  // every score was NaN: still a valid expert
-    total += best;
+    const float chosen = score[at];
+    __syncwarp();  // every lane has read the score before it is struck out
+    total += chosen;
     if (lane == 0) {
       choice[j] = at;
-      weight[j] = best;
-      score[at] = -INFINITY;
+      weight[j] = chosen;
+      pick[at] = -INFINITY;
     }
     __syncwarp();
   }
-  if (renormalize)
-    for (int j = lane; j < top; j += 32) weight[j] /= total + renorm_eps;
+  if (renormalize || scale != 1.f)
+    for (int j = lane; j < top; j += 32) weight[j] = (renormalize ? weight[j] / (total + renorm_eps) : weight[j]) * scale;
 }
 
 // One block per token.  The token's row is staged in shared memory as floats; warp w takes the
@@ -123,11 +132,13 @@ template <typename T>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ router, int* __restrict__ choice,
                  float* __restrict__ weight, int tokens, int hidden, int experts, int top, int softmax_scores,
-                 int renormalize, int groups, int keep, float renorm_eps) {
+                 int renormalize, int groups, int keep, float renorm_eps, const float* __restrict__ correction,
+                 float scale) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
   extern __shared__ float xrow[];  // hidden floats
   __shared__ float all_scores[MAX_EXPERTS];
+  __shared__ float picks[MAX_EXPERTS];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const T* row = x + (size_t)t * ldx;
@@ -139,8 +150,8 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ rou
   }
   __syncthreads();
   if (warp != 0) return;
-  choose_experts(all_scores, experts, top, softmax_scores, renormalize, lane, choice + (size_t)t * top,
-                 weight + (size_t)t * top, groups, keep, renorm_eps);
+  choose_experts(all_scores, correction ? picks : all_scores, correction, experts, top, softmax_scores, renormalize, lane,
+                 choice + (size_t)t * top, weight + (size_t)t * top, groups, keep, renorm_eps, scale);
 }
 
 // plan[0] = tiles in use; plan[1 ..] = expert of every tile (-1: none).
@@ -149,12 +160,14 @@ constexpr int PLAN_NT = 1024;
 __global__ void __launch_bounds__(PLAN_NT)
 moe_plan_kernel(const int* __restrict__ choice, int* __restrict__ position, int* __restrict__ plan, int entries,
                 int experts, int tile, int max_tiles) {
+  // a choice >= experts names an identity expert (its output is its input): it has no row, position -1
   tl::pdl_launch_dependents();
   tl::pdl_wait();
   __shared__ int count[MAX_EXPERTS], start[MAX_EXPERTS], cursor[MAX_EXPERTS];
   for (int e = threadIdx.x; e < experts; e += PLAN_NT) count[e] = cursor[e] = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < entries; i += PLAN_NT) atomicAdd(&count[choice[i]], 1);
+  for (int i = threadIdx.x; i < entries; i += PLAN_NT)
+    if (choice[i] < experts) atomicAdd(&count[choice[i]], 1);
   __syncthreads();
   if (threadIdx.x == 0) {
     int tiles = 0;
@@ -170,7 +183,7 @@ moe_plan_kernel(const int* __restrict__ choice, int* __restrict__ position, int*
   __syncthreads();
   for (int i = threadIdx.x; i < entries; i += PLAN_NT) {
     const int e = choice[i];
-    position[i] = start[e] + atomicAdd(&cursor[e], 1);
+    position[i] = e < experts ? start[e] + atomicAdd(&cursor[e], 1) : -1;
   }
 }
 
@@ -183,6 +196,7 @@ moe_scatter_kernel(const T* __restrict__ x, int ldx, const int* __restrict__ pos
   const int entry = blockIdx.x;
   const int t = entry / top;
   const float w = weighted ? weight[entry] : 1.f;
+  if (position[entry] < 0) return;  // an identity expert has no row
   const T* from = x + (size_t)t * ldx;
   T* to = sorted + (size_t)position[entry] * hidden;
   for (int k = threadIdx.x; k < hidden; k += 128) to[k] = weighted ? from_float<T>(w * to_float(from[k])) : from[k];
@@ -283,7 +297,8 @@ moe_gemm_simt_kernel(const T* __restrict__ x, const T* __restrict__ w, OutT* __r
 template <bool VEC>
 __global__ void __launch_bounds__(128)
 moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ position, const float* __restrict__ weight,
-                   float* __restrict__ side, int hidden, int top, int weighted) {
+                   float* __restrict__ side, int hidden, int top, int weighted, const float* __restrict__ x_f32,
+                   const __nv_bfloat16* __restrict__ x_bf16, int ldx) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
   const int t = blockIdx.x;
@@ -294,8 +309,18 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ position
 #pragma unroll
   for (int i = 0; i < PER; ++i) sum[i] = 0.f;
   for (int j = 0; j < top; ++j) {  // in the order of the choices
-    const float* row = y + (size_t)position[(size_t)t * top + j] * hidden + c;
+    const int at = position[(size_t)t * top + j];
     const float w = weighted ? weight[(size_t)t * top + j] : 1.f;
+    if (at < 0) {  // an identity expert: its output is the token's own input row (x_f32 or x_bf16)
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const size_t e = (size_t)t * ldx + c + i;
+        const float v = x_bf16 ? to_float(x_bf16[e]) : x_f32[e];
+        sum[i] = weighted ? fmaf(w, v, sum[i]) : sum[i] + v;
+      }
+      continue;
+    }
+    const float* row = y + (size_t)at * hidden + c;
     if constexpr (VEC) {
       const float4 v = *reinterpret_cast<const float4*>(row);
       sum[0] = weighted ? fmaf(w, v.x, sum[0]) : sum[0] + v.x;
@@ -323,9 +348,10 @@ extern "C" {
 int tl_moe_tile_rows() { return BM; }
 
 // choice int32 [tokens, top], weight float32 [tokens, top]; router float32 [experts, hidden].
+// correction (optional, float32 [experts]): added to the scores for the choice only.  scale: multiplies the weights.
 int tl_moe_route(const void* x, int ldx, int dtype, const float* router, int* choice, float* weight, int tokens,
                  int hidden, int experts, int top, int softmax_scores, int renormalize, int groups, int keep,
-                 float renorm_eps, cudaStream_t stream) {
+                 float renorm_eps, const float* correction, float scale, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (experts <= 0 || experts > MAX_EXPERTS || top <= 0 || top > experts) return TL_ERR_UNSUPPORTED;
   if (groups < 1 || keep < 1 || keep > groups || experts % groups || top > keep * (experts / groups) || groups > 2048)
@@ -335,11 +361,12 @@ int tl_moe_route(const void* x, int ldx, int dtype, const float* router, int* ch
   if (smem > 48 * 1024) return TL_ERR_UNSUPPORTED;
   if (dtype == TL_DTYPE_F32)
     tl::launch_kernel(moe_route_kernel<float>, blocks, ROUTE_WARPS * 32, smem, stream, (const float*)x, ldx, router, choice,
-                      weight, tokens, hidden, experts, top, softmax_scores, renormalize, groups, keep, renorm_eps);
+                      weight, tokens, hidden, experts, top, softmax_scores, renormalize, groups, keep, renorm_eps, correction,
+                      scale);
   else
     tl::launch_kernel(moe_route_kernel<__nv_bfloat16>, blocks, ROUTE_WARPS * 32, smem, stream, (const __nv_bfloat16*)x,
                       ldx, router, choice, weight, tokens, hidden, experts, top, softmax_scores, renormalize, groups, keep,
-                      renorm_eps);
+                      renorm_eps, correction, scale);
   return TL_LAUNCH_CHECK();
 }
 
@@ -387,19 +414,23 @@ int tl_moe_gemm_simt(const void* x, const void* w, int dtype, void* out, int out
   return TL_LAUNCH_CHECK();
 }
 
+// x (optional; its rows in ``x_dtype``, row stride ldx): the tokens' input rows, which a choice without a row (position
+// -1, an identity expert) adds instead of a product's row.
 int tl_moe_combine(const float* y, const int* position, const float* weight, float* side, int tokens, int hidden,
-                   int top, int weighted, cudaStream_t stream) {
+                   int top, int weighted, const void* x, int ldx, int x_dtype, cudaStream_t stream) {
   if (tokens <= 0) return 0;
+  const float* x_f32 = x && x_dtype == TL_DTYPE_F32 ? (const float*)x : nullptr;
+  const __nv_bfloat16* x_bf16 = x && x_dtype == TL_DTYPE_BF16 ? (const __nv_bfloat16*)x : nullptr;
   const bool vec = hidden % 4 == 0 && ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(side)) & 15) == 0;
   const int per_block = vec ? 512 : 128;
   const unsigned blocks_y = (unsigned)((hidden + per_block - 1) / per_block);
   if (blocks_y > 65535) return TL_ERR_UNSUPPORTED;
   if (vec)
     tl::launch_kernel(moe_combine_kernel<true>, dim3((unsigned)tokens, blocks_y), 128, 0, stream, y, position, weight, side,
-                      hidden, top, weighted);
+                      hidden, top, weighted, x_f32, x_bf16, ldx);
   else
     tl::launch_kernel(moe_combine_kernel<false>, dim3((unsigned)tokens, blocks_y), 128, 0, stream, y, position, weight, side,
-                      hidden, top, weighted);
+                      hidden, top, weighted, x_f32, x_bf16, ldx);
   return TL_LAUNCH_CHECK();
 }
 

@@ -1,0 +1,249 @@
+// The kernels around a selective state-space mixer (state-space duality) and around linear attention with
+// an activation on q, k, v.  The recurrence itself is the scan of gla.cu (a D x V float32 state per head with one
+// decay number per token and head); here is everything before and behind it, all float32 inside:
+//
+//   conv        the causal convolution over time of the channels [x | B | C] (weights [channels, taps], the LAST
+//               column is the current token's; a bias), silu, the step size dt = softplus(dt_raw + bias) and the decay
+//               exp(-exp(A_log) dt) of every head; writes the scan's rows [C (G N) | B (G N) | dt x (H V)], the
+//               activated x and the decays.  Inputs before a step's first token of a request come from the request's
+//               slot (the last taps - 1 raw inputs), zeros before the start of a sequence;
+//   conv_state  moves the last taps - 1 raw inputs of every request into its slot;
+//   gated_norm  out = norm(y) * w with y = o (+ D_h x) and a gate: either y * act(gate) before the norm, or the norm
+//               first and the gate behind it; the norm is an RMS norm over ``groups`` equal parts of the row;
+//   activate    silu, in place, on the first columns of float32 rows;
+//   gate_mul    rows *= sigmoid(gate rows), in the compute type;
+//   token_gate  one number a token: sigmoid(w . x), float32.
+//
+// proj[t] = [ z (inner) | x B C (inner + 2 G N) | dt (H) ] are the float32 rows of the input product.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+using namespace tl;
+
+constexpr int NT = 256;
+constexpr int MAX_TAPS = 8;
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+
+// grid (tokens, ceil(channels / NT)).  channels = inner + 2 G N.
+__global__ void __launch_bounds__(NT)
+ssm_conv_kernel(const float* __restrict__ proj, int proj_stride, int xbc_offset, int dt_offset,
+                const float* __restrict__ weight, const float* __restrict__ bias, const float* __restrict__ dt_bias,
+                const float* __restrict__ a_log, const float* __restrict__ state, const int* __restrict__ token_req,
+                const int* __restrict__ req_indptr, const int* __restrict__ slots, float* __restrict__ scan_in,
+                float* __restrict__ x_out, float* __restrict__ decay, int channels, int taps, int heads, int vdim,
+                int gn, int max_slots) {
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * NT + threadIdx.x;
+  const int req = token_req[t];
+  const int slot = slots[req];
+  const bool live = TL_DEBUG_OK(slot >= -1 && slot < max_slots, TL_DEBUG_SLOT, slot) && slot >= 0;
+  const int inner = heads * vdim;
+  const int scan_row = 2 * gn + inner;
+  if (blockIdx.y == 0 && threadIdx.x < heads) {
+    const int h = threadIdx.x;
+    const float dt = softplus_f(proj[(size_t)t * proj_stride + dt_offset + h] + dt_bias[h]);
+    decay[(size_t)t * heads + h] = live ? expf(-expf(a_log[h]) * dt) : 1.f;
+  }
+  if (c >= channels) return;
+  float sum = bias[c];
+  if (live) {
+    const int i = t - req_indptr[req];  // the token's place in its request's portion
+    const float* old = state + (size_t)slot * (taps - 1) * channels;
+    for (int j = 0; j < taps; ++j) {  // ascending j: oldest input first
+      const int back = taps - 1 - j;
+      const float v = i - back >= 0 ? proj[(size_t)(t - back) * proj_stride + xbc_offset + c]
+                                    : old[(size_t)(taps - 1 + i - back) * channels + c];
+      sum = fmaf(weight[(size_t)c * taps + j], v, sum);
+    }
+  }
+  const float act = live ? silu_f(sum) : 0.f;
+  if (c < inner) {
+    const int h = c / vdim;
+    const float dt = softplus_f(proj[(size_t)t * proj_stride + dt_offset + h] + dt_bias[h]);
+    x_out[(size_t)t * inner + c] = act;
+    scan_in[(size_t)t * scan_row + 2 * gn + c] = dt * act;
+  } else if (c < inner + gn) {
+    scan_in[(size_t)t * scan_row + gn + (c - inner)] = act;  // B: the scan's k
+  } else {
+    scan_in[(size_t)t * scan_row + (c - inner - gn)] = act;  // C: the scan's q
+  }
+}
+
+// grid (requests, ceil(channels / NT)); a thread moves one channel's rows, oldest first, so that a row of the old state
+// is read before the same thread overwrites it.
+__global__ void __launch_bounds__(NT)
+ssm_conv_state_kernel(const float* __restrict__ proj, int proj_stride, int xbc_offset, float* __restrict__ state,
+                      const int* __restrict__ req_indptr, const int* __restrict__ slots, int channels, int taps,
+                      int max_slots) {
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+  const int req = blockIdx.x;
+  const int c = blockIdx.y * NT + threadIdx.x;
+  const int slot = slots[req];
+  if (!(TL_DEBUG_OK(slot >= -1 && slot < max_slots, TL_DEBUG_SLOT, slot) && slot >= 0) || c >= channels) return;
+  const int first = req_indptr[req], n = req_indptr[req + 1] - first;
+  float* rows = state + (size_t)slot * (taps - 1) * channels;
+  for (int j = 0; j < taps - 1; ++j) {
+    const int from = n - (taps - 1) + j;  // index into the portion; negative: a row of the old state
+    rows[(size_t)j * channels + c] = from >= 0 ? proj[(size_t)(first + from) * proj_stride + xbc_offset + c]
+                                               : rows[(size_t)(taps - 1 + from) * channels + c];
+  }
+}
+
+// grid (tokens, groups).  y = o + skip[h] x (skip, x optional); gate_first: y *= act(gate), then the norm and the weight;
+// else the norm and the weight, then *= act(gate).  gate_act: 0 silu, 1 sigmoid.  The gate is float32 rows.
+template <typename T>
+__global__ void __launch_bounds__(NT)
+gated_norm_kernel(const float* __restrict__ o, const float* __restrict__ x, const float* __restrict__ skip,
+                  const float* __restrict__ gate, int gate_stride, const float* __restrict__ weight,
+                  T* __restrict__ out, int width, int groups, int vdim, int gate_first, int gate_act, float eps) {
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+  __shared__ float scratch[32];
+  const int t = blockIdx.x, part = width / groups, c0 = blockIdx.y * part;
+  const float* row = o + (size_t)t * width;
+  const float* g = gate + (size_t)t * gate_stride;
+  auto value = [&](int c) {
+    float y = row[c];
+    if (skip) y = fmaf(skip[c / vdim], x[(size_t)t * width + c], y);
+    if (gate_first) y *= gate_act ? sigmoid_f(g[c]) : silu_f(g[c]);
+    return y;
+  };
+  float ss = 0.f;
+  for (int c = c0 + threadIdx.x; c < c0 + part; c += NT) {
+    const float y = value(c);
+    ss = fmaf(y, y, ss);
+  }
+  ss = block_sum<NT>(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)part + eps);
+  for (int c = c0 + threadIdx.x; c < c0 + part; c += NT) {
+    float y = value(c) * inv * weight[c];
+    if (!gate_first) y *= gate_act ? sigmoid_f(g[c]) : silu_f(g[c]);
+    out[(size_t)t * width + c] = from_float<T>(y);
+  }
+}
+
+__global__ void activate_kernel(float* __restrict__ rows, int stride, int cols, size_t total) {
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= total) return;
+  float* at = rows + (e / cols) * stride + e % cols;
+  *at = silu_f(*at);
+}
+
+template <typename T>
+__global__ void gate_mul_kernel(T* __restrict__ rows, const float* __restrict__ gate, int gate_stride, int cols,
+                                size_t total) {
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= total) return;
+  const size_t t = e / cols;
+  const int c = (int)(e % cols);
+  rows[e] = from_float<T>(to_float(rows[e]) * sigmoid_f(gate[t * gate_stride + c]));
+}
+
+// One warp a token: out[t] = sigmoid(w . x[t]); each lane sums its 32nd in ascending k.
+template <typename T>
+__global__ void __launch_bounds__(128)
+token_gate_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w, float* __restrict__ out, int tokens,
+                  int hidden) {
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= tokens) return;
+  const T* row = x + (size_t)t * ldx;
+  float sum = 0.f;
+  for (int k = lane; k < hidden; k += 32) sum = fmaf(to_float(row[k]), w[k], sum);
+  sum = warp_sum(sum);
+  if (lane == 0) out[t] = sigmoid_f(sum);
+}
+
+}  // namespace
+
+TL_DEBUG_READER(tl_ssm_debug_error)
+
+extern "C" {
+
+// scan_in float32 [tokens, 2 G N + H V]; x_out float32 [tokens, H V]; decay float32 [tokens, H];
+// state float32 [max_slots, taps - 1, channels] (unused when taps == 1).
+int tl_ssm_conv(const float* proj, int proj_stride, int xbc_offset, int dt_offset, const float* weight, const float* bias,
+                const float* dt_bias, const float* a_log, const float* state, const int* token_req,
+                const int* req_indptr, const int* slots, float* scan_in, float* x_out, float* decay, int tokens,
+                int taps, int heads, int vdim, int gn, int max_slots, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (taps < 1 || taps > MAX_TAPS || heads <= 0 || heads > NT || vdim <= 0 || gn <= 0) return TL_ERR_UNSUPPORTED;
+  const int channels = heads * vdim + 2 * gn;
+  dim3 grid(tokens, (channels + NT - 1) / NT);
+  tl::launch_kernel(ssm_conv_kernel, grid, NT, 0, stream, proj, proj_stride, xbc_offset, dt_offset, weight, bias, dt_bias,
+                    a_log, state, token_req, req_indptr, slots, scan_in, x_out, decay, channels, taps, heads, vdim, gn,
+                    max_slots);
+  return TL_LAUNCH_CHECK();
+}
+
+int tl_ssm_conv_state(const float* proj, int proj_stride, int xbc_offset, float* state, const int* req_indptr,
+                      const int* slots, int requests, int channels, int taps, int max_slots, cudaStream_t stream) {
+  if (requests <= 0 || taps <= 1) return 0;
+  if (taps > MAX_TAPS) return TL_ERR_UNSUPPORTED;
+  dim3 grid(requests, (channels + NT - 1) / NT);
+  tl::launch_kernel(ssm_conv_state_kernel, grid, NT, 0, stream, proj, proj_stride, xbc_offset, state, req_indptr, slots,
+                    channels, taps, max_slots);
+  return TL_LAUNCH_CHECK();
+}
+
+int tl_gated_norm(const float* o, const float* x, const float* skip, const float* gate, int gate_stride,
+                  const float* weight, void* out, int out_dtype, int tokens, int width, int groups, int vdim,
+                  int gate_first, int gate_act, float eps, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (groups <= 0 || width % groups || groups > 65535 || vdim <= 0) return TL_ERR_UNSUPPORTED;
+  dim3 grid(tokens, groups);
+  if (out_dtype == TL_DTYPE_F32)
+    tl::launch_kernel(gated_norm_kernel<float>, grid, NT, 0, stream, o, x, skip, gate, gate_stride, weight, (float*)out,
+                      width, groups, vdim, gate_first, gate_act, eps);
+  else
+    tl::launch_kernel(gated_norm_kernel<__nv_bfloat16>, grid, NT, 0, stream, o, x, skip, gate, gate_stride, weight,
+                      (__nv_bfloat16*)out, width, groups, vdim, gate_first, gate_act, eps);
+  return TL_LAUNCH_CHECK();
+}
+
+int tl_activate_silu(float* rows, int stride, int tokens, int cols, cudaStream_t stream) {
+  const size_t total = (size_t)tokens * cols;
+  if (total == 0) return 0;
+  tl::launch_kernel(activate_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, rows, stride, cols, total);
+  return TL_LAUNCH_CHECK();
+}
+
+int tl_gate_mul(void* rows, int dtype, const float* gate, int gate_stride, int tokens, int cols, cudaStream_t stream) {
+  const size_t total = (size_t)tokens * cols;
+  if (total == 0) return 0;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == TL_DTYPE_F32)
+    tl::launch_kernel(gate_mul_kernel<float>, blocks, 256, 0, stream, (float*)rows, gate, gate_stride, cols, total);
+  else
+    tl::launch_kernel(gate_mul_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)rows, gate, gate_stride,
+                      cols, total);
+  return TL_LAUNCH_CHECK();
+}
+
+int tl_token_gate(const void* x, int ldx, int dtype, const float* w, float* out, int tokens, int hidden,
+                  cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  const unsigned blocks = (unsigned)((tokens + 3) / 4);
+  if (dtype == TL_DTYPE_F32)
+    tl::launch_kernel(token_gate_kernel<float>, blocks, 128, 0, stream, (const float*)x, ldx, w, out, tokens, hidden);
+  else
+    tl::launch_kernel(token_gate_kernel<__nv_bfloat16>, blocks, 128, 0, stream, (const __nv_bfloat16*)x, ldx, w, out,
+                      tokens, hidden);
+  return TL_LAUNCH_CHECK();
+}
+
+}  // extern "C"

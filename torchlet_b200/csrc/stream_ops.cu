@@ -6,6 +6,7 @@
 //   rms_scaled_add    acc += m * y / sqrt(mean(y^2) + eps) * w      (a normed side branch)
 //   gated_token_embed out = gelu_tanh(gate) * table[token]          (gate of a per-token input)
 //   clamped_glu       out = g sigmoid(alpha g) (u + 1),  g = min(gate, limit), u = clamp(up, +-limit)
+//   glu_act           out = act(gate) * up (* one number a token), act = silu or the tanh form of gelu
 //   scale             x *= alpha                  (logit scale)
 //   fill_zero
 //
@@ -186,6 +187,24 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out
   out[idx] = from_float<T>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
 }
 
+// act: 0 silu(g) = g sigmoid(g); 1 the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))).
+// row_scale (optional, float32 [tokens]): the row is multiplied by its token's number before it is rounded.
+template <typename T>
+__global__ void glu_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total, int act,
+                               const float* __restrict__ row_scale) {
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const size_t t = idx / inter;
+  const int j = (int)(idx - t * inter);
+  const float g = to_float(gu[t * 2 * inter + j]);
+  const float u = to_float(gu[t * 2 * inter + inter + j]);
+  const float a = act == 1 ? 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))
+                           : g / (1.f + expf(-g));
+  out[idx] = from_float<T>(a * u * (row_scale ? row_scale[t] : 1.f));
+}
+
 }  // namespace
 
 TL_DEBUG_READER(tl_stream_ops_debug_error)
@@ -271,6 +290,21 @@ int tl_clamped_glu(const void* gate_up, void* out, int dtype, int tokens, int in
   else
     tl::launch_kernel(clamped_glu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gate_up,
                       (__nv_bfloat16*)out, inter, total, limit, alpha);
+  return TL_LAUNCH_CHECK();
+}
+
+int tl_glu_act(const void* gate_up, void* out, int dtype, int tokens, int inter, int act, const float* row_scale,
+               cudaStream_t stream) {
+  const size_t total = (size_t)tokens * inter;
+  if (total == 0) return 0;
+  if (act < 0 || act > 1) return TL_ERR_UNSUPPORTED;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == TL_DTYPE_F32)
+    tl::launch_kernel(glu_act_kernel<float>, blocks, 256, 0, stream, (const float*)gate_up, (float*)out, inter, total,
+                      act, row_scale);
+  else
+    tl::launch_kernel(glu_act_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gate_up,
+                      (__nv_bfloat16*)out, inter, total, act, row_scale);
   return TL_LAUNCH_CHECK();
 }
 

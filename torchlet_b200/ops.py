@@ -106,6 +106,7 @@ _SIGNATURES = {
                                        c_void_p],
         "tl_gated_token_embed": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
         "tl_clamped_glu": [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p],
+        "tl_glu_act": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "tl_stream_ops_debug_error": [c_void_p],
     },
     "delta_rule": {
@@ -138,7 +139,7 @@ _SIGNATURES = {
     "gla": {
         "tl_gla_decay": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
         "tl_gla_scan": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                        c_int, c_float, c_int, c_void_p],
+                        c_int, c_int, c_float, c_int, c_void_p],
         "tl_rotate_heads_f32": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "tl_gla_finish": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
                           c_void_p],
@@ -153,12 +154,24 @@ _SIGNATURES = {
     "moe": {
         "tl_moe_tile_rows": [],
         "tl_moe_route": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                         c_int, c_int, c_float, c_void_p],
+                         c_int, c_int, c_float, c_void_p, c_float, c_void_p],
         "tl_moe_plan": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "tl_moe_scatter": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "tl_moe_gemm_simt": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float,
                              c_float, c_void_p],
-        "tl_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "tl_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int,
+                           c_void_p],
+    },
+    "ssm": {
+        "tl_ssm_conv": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "tl_ssm_conv_state": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "tl_gated_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                          c_int, c_int, c_int, c_float, c_void_p],
+        "tl_activate_silu": [c_void_p, c_int, c_int, c_int, c_void_p],
+        "tl_gate_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+        "tl_token_gate": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "tl_ssm_debug_error": [c_void_p],
     },
     "hyper": {
         "tl_hyper_fanout": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -484,19 +497,24 @@ def gla_decay(proj, low_offset: int, w2t, bias, decay, rank: int, tau: float) ->
 
 
 def gla_scan(proj, decay, req_indptr, slots, state, out, requests: int, heads: int, dim: int, vdim: int,
-             qscale: float, fixed_decay: bool = False) -> None:
+             qscale: float, fixed_decay: bool = False, token_decay: bool = False, qk_heads: int | None = None) -> None:
     """Walks each request's tokens of the step through its slot's state [H, D, V] (float32):
-    S = diag(decay) S + k v^T, out = S^T q * qscale; ``proj`` rows are [q (H D) | k (H D) | v (H V) | ...].
-    ``decay`` is float32 [tokens, H D], or with ``fixed_decay`` one constant per head, [H] (a retention).
+    S = diag(decay) S + k v^T, out = S^T q * qscale; ``proj`` rows are [q (G D) | k (G D) | v (H V) | ...] with
+    G = ``qk_heads`` (default H) heads of q and k, head h reading q/k head h // (H / G).
+    ``decay`` is float32 [tokens, H D] (one number a key channel), or with ``fixed_decay`` one constant per head, [H]
+    (a retention), or with ``token_decay`` [tokens, H] (one number a token and head).
     A request whose slot is negative is padding."""
     _need_cuda(proj, decay, req_indptr, slots, state, out)
     assert proj.dtype == decay.dtype == state.dtype == out.dtype == torch.float32
-    assert decay.numel() == (heads if fixed_decay else proj.shape[0] * heads * dim)
+    assert not (fixed_decay and token_decay)
+    qk_heads = heads if qk_heads is None else int(qk_heads)
+    assert decay.numel() == (heads if fixed_decay else proj.shape[0] * heads * (1 if token_decay else dim))
     assert state.is_contiguous() and out.is_contiguous() and decay.is_contiguous() and proj.stride(1) == 1
     assert state.shape[1:] == (heads, dim, vdim) and req_indptr.dtype == slots.dtype == torch.int32
     code = _fn("gla", "tl_gla_scan")(proj.data_ptr(), proj.stride(0), decay.data_ptr(), req_indptr.data_ptr(),
-                                     slots.data_ptr(), state.data_ptr(), out.data_ptr(), requests, heads, dim, vdim,
-                                     state.shape[0], float(qscale), 1 if fixed_decay else 0, _stream())
+                                     slots.data_ptr(), state.data_ptr(), out.data_ptr(), requests, heads, qk_heads, dim,
+                                     vdim, state.shape[0], float(qscale), 1 if fixed_decay else (2 if token_decay else 0),
+                                     _stream())
     _check(code, "gla_scan")
 
 
@@ -698,6 +716,97 @@ def pooled_prior(q, token_req, positions, slots, pooled, ml, acc, nh: int, nkv: 
     _check(code, "pooled_prior")
 
 
+# ------------------------------------------- state-space mixer, gated norms, gates
+GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def glu_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu", row_scale=None) -> None:
+    """out = act(gate) * up over rows [gate (I) | up (I)], act "silu" or "gelu_tanh"; ``row_scale`` (float32 [tokens]):
+    every row is multiplied by its token's number before it is rounded."""
+    _need_cuda(gate_up, out, row_scale)
+    tokens, inter = out.shape
+    assert gate_up.is_contiguous() and out.is_contiguous() and gate_up.shape == (tokens, 2 * inter) and gate_up.dtype == out.dtype
+    assert row_scale is None or (row_scale.dtype == torch.float32 and row_scale.numel() == tokens)
+    code = _fn("stream_ops", "tl_glu_act")(gate_up.data_ptr(), out.data_ptr(), dtype_code(out.dtype), tokens, inter,
+                                           GLU_ACTIVATIONS[activation], _ptr(row_scale), _stream())
+    _check(code, "glu_act")
+
+
+def ssm_conv(proj, xbc_offset: int, dt_offset: int, weight, bias, dt_bias, a_log, state, token_req, req_indptr, slots,
+             scan_in, x_out, decay, heads: int, vdim: int, gn: int) -> None:
+    """The front of a selective state-space mixer (csrc/ssm.cu): causal convolution over time of the channels
+    proj[:, xbc_offset:] = [x (H V) | B (G N) | C (G N)] with ``weight`` [channels, taps] (last column: the current
+    token) and ``bias``, silu; dt = softplus(proj[:, dt_offset:] + dt_bias); writes the scan's rows
+    ``scan_in`` [C | B | dt x], ``x_out`` and ``decay`` [tokens, H] = exp(-exp(a_log) dt).  ``state`` [slots, taps - 1,
+    channels] holds each request's last raw inputs (None when taps == 1)."""
+    _need_cuda(proj, weight, bias, dt_bias, a_log, state, token_req, req_indptr, slots, scan_in, x_out, decay)
+    tokens = proj.shape[0]
+    channels, taps = weight.shape
+    assert channels == heads * vdim + 2 * gn and proj.dtype == torch.float32 and proj.stride(1) == 1
+    assert all(t.dtype == torch.float32 and t.is_contiguous() for t in (weight, bias, dt_bias, a_log, scan_in, x_out, decay))
+    assert scan_in.shape == (tokens, 2 * gn + heads * vdim) and x_out.shape == (tokens, heads * vdim) and decay.shape == (tokens, heads)
+    assert taps == 1 or (state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (taps - 1, channels))
+    code = _fn("ssm", "tl_ssm_conv")(proj.data_ptr(), proj.stride(0), xbc_offset, dt_offset, weight.data_ptr(), bias.data_ptr(),
+                                     dt_bias.data_ptr(), a_log.data_ptr(), _ptr(state), token_req.data_ptr(),
+                                     req_indptr.data_ptr(), slots.data_ptr(), scan_in.data_ptr(), x_out.data_ptr(),
+                                     decay.data_ptr(), tokens, taps, heads, vdim, gn, state.shape[0] if state is not None else 0,
+                                     _stream())
+    _check(code, "ssm_conv")
+
+
+def ssm_conv_state(proj, xbc_offset: int, state, req_indptr, slots, requests: int) -> None:
+    """Moves the last taps - 1 raw inputs proj[:, xbc_offset : xbc_offset + channels] of every request into its slot's
+    rows of ``state`` [slots, taps - 1, channels] (rows of the old state where the portion is shorter)."""
+    _need_cuda(proj, state, req_indptr, slots)
+    assert proj.dtype == state.dtype == torch.float32 and state.is_contiguous() and proj.stride(1) == 1
+    code = _fn("ssm", "tl_ssm_conv_state")(proj.data_ptr(), proj.stride(0), xbc_offset, state.data_ptr(), req_indptr.data_ptr(),
+                                           slots.data_ptr(), requests, state.shape[2], state.shape[1] + 1, state.shape[0],
+                                           _stream())
+    _check(code, "ssm_conv_state")
+
+
+def gated_norm(o, gate, weight, out, groups: int, eps: float, gate_first: bool, gate_act: str, x=None, skip=None,
+               vdim: int = 1) -> None:
+    """out = rmsnorm_groups(y) * weight with a gate: y = o (+ skip[c // vdim] * x), ``gate_first``: y * act(gate) goes
+    through the norm, else the normed and weighted row is multiplied by act(gate).  ``gate``: float32 rows (a view);
+    act "silu" or "sigmoid"; the RMS norm is taken over ``groups`` equal parts of the row; all float32 inside."""
+    _need_cuda(o, gate, weight, out, x, skip)
+    tokens, width = o.shape
+    assert o.dtype == gate.dtype == weight.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous()
+    assert gate.stride(1) == 1 and gate.shape == o.shape == out.shape and weight.numel() == width
+    assert (x is None) == (skip is None) and (x is None or (x.dtype == torch.float32 and x.is_contiguous() and x.shape == o.shape))
+    code = _fn("ssm", "tl_gated_norm")(o.data_ptr(), _ptr(x), _ptr(skip), gate.data_ptr(), gate.stride(0), weight.data_ptr(),
+                                       out.data_ptr(), dtype_code(out.dtype), tokens, width, int(groups), int(vdim),
+                                       1 if gate_first else 0, {"silu": 0, "sigmoid": 1}[gate_act], float(eps), _stream())
+    _check(code, "gated_norm")
+
+
+def activate_silu_(rows, cols: int) -> None:
+    """silu, in place, on the first ``cols`` columns of float32 rows."""
+    _need_cuda(rows)
+    assert rows.dtype == torch.float32 and rows.stride(1) == 1 and cols <= rows.shape[1]
+    _check(_fn("ssm", "tl_activate_silu")(rows.data_ptr(), rows.stride(0), rows.shape[0], cols, _stream()), "activate_silu")
+
+
+def gate_mul_(rows, gate) -> None:
+    """rows *= sigmoid(gate): ``rows`` contiguous in the compute type, ``gate`` float32 rows (a view) of the same shape."""
+    _need_cuda(rows, gate)
+    assert rows.is_contiguous() and gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape == rows.shape
+    code = _fn("ssm", "tl_gate_mul")(rows.data_ptr(), dtype_code(rows.dtype), gate.data_ptr(), gate.stride(0), rows.shape[0],
+                                     rows.shape[1], _stream())
+    _check(code, "gate_mul")
+
+
+def token_gate(x, w, out) -> None:
+    """out[t] = sigmoid(w . x[t]) in float32; ``w`` float32 [hidden]."""
+    _need_cuda(x, w, out)
+    tokens, hidden = x.shape
+    assert w.dtype == out.dtype == torch.float32 and w.numel() == hidden and out.numel() == tokens and x.stride(1) == 1
+    code = _fn("ssm", "tl_token_gate")(x.data_ptr(), x.stride(0), dtype_code(x.dtype), w.data_ptr(), out.data_ptr(), tokens,
+                                       hidden, _stream())
+    _check(code, "token_gate")
+
+
 # ------------------------------------------------------- routed feed-forward
 def moe_tile_rows() -> int:
     """Rows of a tile of the grouped CUDA-core products (every expert's rows are padded to whole tiles)."""
@@ -705,25 +814,29 @@ def moe_tile_rows() -> int:
 
 
 def moe_route(x, router, choice, weight, softmax_scores: bool = False, renormalize: bool = False, groups: int = 1,
-              keep: int = 1, renorm_eps: float = 0.0) -> None:
+              keep: int = 1, renorm_eps: float = 0.0, correction=None, scale: float = 1.0) -> None:
     """choice[t, j], weight[t, j]: the ``top`` experts of every token by score (sigmoid or softmax of the
     float32 router logits) and their scores (csrc/moe.cu), divided by their sum + ``renorm_eps`` if
     ``renormalize``.  ``groups`` > 1: the experts form that many equal groups of neighbours and only experts of the
-    ``keep`` groups with the largest best score can be chosen."""
-    _need_cuda(x, router, choice, weight)
+    ``keep`` groups with the largest best score can be chosen.  ``correction`` (float32 [experts]): the choice goes
+    by score + correction, the weights stay the scores.  ``scale`` multiplies the weights."""
+    _need_cuda(x, router, choice, weight, correction)
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == router.shape[0])
     tokens, hidden = x.shape
     experts, top = router.shape[0], choice.shape[1]
     assert router.dtype == torch.float32 and router.is_contiguous() and router.shape[1] == hidden and x.stride(1) == 1
     assert choice.dtype == torch.int32 and weight.dtype == torch.float32 and choice.is_contiguous() and weight.is_contiguous()
     code = _fn("moe", "tl_moe_route")(x.data_ptr(), x.stride(0), dtype_code(x.dtype), router.data_ptr(), choice.data_ptr(),
                                       weight.data_ptr(), tokens, hidden, experts, top, 1 if softmax_scores else 0,
-                                      1 if renormalize else 0, int(groups), int(keep), float(renorm_eps), _stream())
+                                      1 if renormalize else 0, int(groups), int(keep), float(renorm_eps), _ptr(correction),
+                                      float(scale), _stream())
     _check(code, "moe_route")
 
 
 def moe_plan(choice, position, plan, experts: int, tile: int) -> None:
     """position[t, j]: the row of (token, choice) in the expert-sorted order, every expert's rows padded to
-    whole tiles of ``tile`` rows; plan[0] tiles in use, plan[1 + i] the expert of tile i."""
+    whole tiles of ``tile`` rows; plan[0] tiles in use, plan[1 + i] the expert of tile i.  A choice >= ``experts``
+    (an identity expert) has no row: its position is -1."""
     _need_cuda(choice, position, plan)
     assert position.dtype == plan.dtype == torch.int32 and position.numel() == choice.numel()
     code = _fn("moe", "tl_moe_plan")(choice.data_ptr(), position.data_ptr(), plan.data_ptr(), choice.numel(), experts, tile,
@@ -755,13 +868,16 @@ def moe_gemm_simt(x, w, out, plan, glu: bool = False, limit: float = 0.0, alpha:
     _check(code, "moe_gemm_simt")
 
 
-def moe_combine(y, position, weight, side, top: int, weighted: bool) -> None:
-    """side[t] += sum_j y[position[t, j]] (* weight[t, j] if ``weighted``), float32, in the order of j."""
-    _need_cuda(y, position, weight, side)
+def moe_combine(y, position, weight, side, top: int, weighted: bool, x=None) -> None:
+    """side[t] += sum_j y[position[t, j]] (* weight[t, j] if ``weighted``), float32, in the order of j.  Where a
+    position is -1 (an identity expert) the token's own row of ``x`` stands for the product's row."""
+    _need_cuda(y, position, weight, side, x)
     tokens, hidden = side.shape
     assert y.dtype == side.dtype == torch.float32 and y.is_contiguous() and side.is_contiguous() and y.shape[1] == hidden
+    assert x is None or (x.shape == (tokens, hidden) and x.stride(1) == 1)
     code = _fn("moe", "tl_moe_combine")(y.data_ptr(), position.data_ptr(), weight.data_ptr(), side.data_ptr(), tokens,
-                                        hidden, top, 1 if weighted else 0, _stream())
+                                        hidden, top, 1 if weighted else 0, _ptr(x), x.stride(0) if x is not None else 0,
+                                        dtype_code(x.dtype) if x is not None else 0, _stream())
     _check(code, "moe_combine")
 
 
@@ -774,13 +890,13 @@ def latent_prepare(down, q_rank, kv_rank, rot_dim, rot_dims, q_norm, kv_norm, in
     tokens = down.shape[0]
     assert down.dtype == torch.float32 and down.stride(1) == 1
     assert down.shape[1] == q_rank + ((kv_rank + rot_dim) if write_kv else 0)
-    assert q_latent.is_contiguous() and q_latent.shape == (tokens, q_rank)
-    assert not write_kv or (pages.dtype == q_latent.dtype and pages.is_contiguous())
+    assert q_rank == 0 or (q_latent.is_contiguous() and q_latent.shape == (tokens, q_rank))
+    assert not write_kv or ((q_latent is None or pages.dtype == q_latent.dtype) and pages.is_contiguous())
     code = _fn("latent_attention", "tl_latent_prepare")(
-        down.data_ptr(), down.stride(0), q_rank, kv_rank, rot_dim, rot_dims, q_norm.data_ptr(), _ptr(kv_norm),
+        down.data_ptr(), down.stride(0), q_rank, kv_rank, rot_dim, rot_dims, _ptr(q_norm), _ptr(kv_norm),
         inv_freq.data_ptr(), float(eps), positions.data_ptr(), token_req.data_ptr(), block_table.data_ptr(),
-        block_table.shape[1], pages.data_ptr(), dtype_code(q_latent.dtype), page_size, pages.shape[0],
-        q_latent.data_ptr(), 1 if write_kv else 0, tokens, _stream())
+        block_table.shape[1], pages.data_ptr(), dtype_code(pages.dtype), page_size, pages.shape[0],
+        _ptr(q_latent), 1 if write_kv else 0, tokens, _stream())
     _check(code, "latent_prepare")
 
 
@@ -1202,7 +1318,7 @@ def debug_errors() -> list:
     found = []
     for library in ("elementwise", "attention_generic", "attention_mma", "decode_fused", "slots", "stream_ops",
                     "delta_rule", "latent_attention", "latent_attention_mma", "gla", "gated_attention", "hyper",
-                    "pooled_attention"):
+                    "pooled_attention", "ssm"):
         if any(name in _functions for name in _SIGNATURES[library]):
             value = ctypes.c_int(0)
             code = _fn(library, f"tl_{library}_debug_error")(ctypes.byref(value))

@@ -19,8 +19,8 @@ from .base import (
     TokenInput,
     build_part,
 )
-from . import (attention, block, clamped_glu, delta_rule, gated_attention, gla, latent_attention, norm, parallel_pair,
-               pooled_attention, retention, rotary, routed_glu, swiglu, token_input)  # noqa: F401  (registration)
+from . import (attention, block, clamped_glu, delta_rule, gated_attention, gated_mlp, gla, latent_attention, mamba2, norm,
+               parallel_pair, pooled_attention, retention, rotary, routed_glu, swiglu, token_input)  # noqa: F401  (registration)
 from .linear import Linear
 from .model import LayeredModel, expected_tensors
 

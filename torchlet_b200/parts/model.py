@@ -41,6 +41,8 @@ def _layer_parts(layer) -> list:
 def expected_tensors(spec: ModelSpec) -> list[TensorSpec]:
     """Every tensor the checkpoint must hold, by name, with its shape."""
     out = [TensorSpec(spec.embedding_name, (spec.vocab_size, spec.hidden_size))]
+    if spec.embedding_norm is not None:
+        out += NORMS.get(spec.embedding_norm.kind).expected_tensors(spec.embedding_norm, spec.embedding_norm_prefix)
     for layer in spec.layers:
         for registry, part, prefix, _ in _layer_parts(layer):
             out += registry.get(part.kind).expected_tensors(part, prefix)
@@ -75,6 +77,7 @@ class LayeredModel:
                 )
             )
         self.final_norm = build_part(NORMS, spec.final_norm)
+        self.embedding_norm = build_part(NORMS, spec.embedding_norm) if spec.embedding_norm is not None else None
         self.embedding: torch.Tensor | None = None
         self.lm_head: Linear | None = None
         self.dtype: torch.dtype | None = None
@@ -108,6 +111,8 @@ class LayeredModel:
                 part.load(tensors, prefix, device, dtype)
             block.load(tensors, layer, device, dtype)
         self.final_norm.load(tensors, spec.final_norm_prefix, device, dtype)
+        if self.embedding_norm is not None:
+            self.embedding_norm.load(tensors, spec.embedding_norm_prefix, device, dtype)
         if spec.tie_word_embeddings:
             self.lm_head = Linear.from_device_weight(self.embedding)
         else:
@@ -116,11 +121,26 @@ class LayeredModel:
     # --------------------------------------------------------------- forward
     def forward(self, ctx, caches: list) -> torch.Tensor:
         """Run the step's tokens through the schedule; returns the float32 stream [T, hidden]."""
-        acc = ctx.buffer("stream", (ctx.num_tokens, self.spec.hidden_size), torch.float32)
-        ops.embed(self.embedding, ctx.tokens, acc, self.spec.embedding_scale)
+        shape = (ctx.num_tokens, self.spec.hidden_size)
+        acc = ctx.buffer("stream", shape, torch.float32)
+        again = any(entry.add_embedding for entry in self.spec.schedule)
+        first = ctx.buffer("stream.first", shape, torch.float32) if again else None  # the embedding output, kept
+        if self.embedding_norm is None:
+            ops.embed(self.embedding, ctx.tokens, acc, self.spec.embedding_scale)
+            if again:
+                ops.embed(self.embedding, ctx.tokens, first, self.spec.embedding_scale)
+        else:  # the norm writes float32 rows: the stream stays 32-bit from its first value on
+            raw = ctx.buffer("stream.embedding", shape, torch.float32)
+            ops.embed(self.embedding, ctx.tokens, raw, self.spec.embedding_scale)
+            self.embedding_norm.apply(ctx, raw, out=acc)
+            if again:
+                self.embedding_norm.apply(ctx, raw, out=first)
         streams = self.spec.streams
         if streams is None:
             for i, entry in enumerate(self.spec.schedule):
+                if entry.add_embedding:
+                    ctx.flush_pending()
+                    ops.scaled_add(acc, first, 1.0)
                 self.blocks[entry.layer].forward(ctx, acc, caches[i])
             ctx.flush_pending()
             return acc

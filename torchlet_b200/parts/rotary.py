@@ -61,6 +61,8 @@ def scaled_frequencies(dims: int, base: float, scaling: dict | None) -> tuple:
     freq = float(base) ** (-2.0 * i / dims)
     if not scaling:
         return freq, 1.0
+    if "low" in scaling or "high" in scaling:
+        return wavelength_scaled_frequencies(freq, scaling), 1.0
     factor, original = float(scaling["factor"]), float(scaling["original"])
 
     def pair(turns: float) -> float:
@@ -73,11 +75,41 @@ def scaled_frequencies(dims: int, base: float, scaling: dict | None) -> tuple:
     return freq, 0.1 * math.log(factor) + 1.0
 
 
+def wavelength_scaled_frequencies(freq: torch.Tensor, scaling: dict) -> torch.Tensor:
+    """Frequencies slowed down by wavelength (``scaling``: factor, low, high, original).  With the wavelength
+    l = 2 pi / f: f stays where l < original / high; becomes f / factor where l > original / low; and between the two,
+    with s = (original / l - low) / (high - low), (1 - s) f / factor + s f.  float64 in, float64 out."""
+    import math
+
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+    low, high = float(scaling["low"]), float(scaling["high"])
+    wavelength = 2.0 * math.pi / freq
+    blend = (original / wavelength - low) / (high - low) if high != low else torch.ones_like(freq)
+    mixed = (1.0 - blend) * freq / factor + blend * freq
+    out = torch.where(wavelength > original / low, freq / factor, mixed)
+    return torch.where(wavelength < original / high, freq, out)
+
+
+def pair_permutation(head_dim: int, dims: int, pairing: str) -> list:
+    """The order in which a head's projection rows are laid out so that the kernels' split-half rotation (entry i with
+    i + dims / 2) turns the pairs the checkpoint means.  "split_half": as stored.  "interleaved": the checkpoint pairs
+    entry 2i with 2i + 1, so the even entries of the first ``dims`` come first, then the odd ones.  q and k take the
+    same order, which leaves every q . k as it was."""
+    if pairing == "split_half":
+        return list(range(head_dim))
+    if pairing != "interleaved":
+        raise ValueError(f"unknown pairing {pairing!r} (known: split_half, interleaved)")
+    return list(range(0, dims, 2)) + list(range(1, dims, 2)) + list(range(dims, head_dim))
+
+
 @POSITIONS.register("rotary_partial")
 class RotaryPartial(Positions):
     """Split-half rotation of the FIRST ``dims`` entries of every head (entry i with i + dims / 2; the
     rest pass unchanged), with optional frequency scaling (``scaled_frequencies``).  Parameters:
-    ``head_dim``, ``dims``, ``base``, ``scaling`` (None or factor / original / fast / slow).  The part
+    ``head_dim``, ``dims``, ``base``, ``scaling`` (None, or factor / original / fast / slow for frequencies blended by
+    turns, or factor / original / low / high for frequencies slowed down by wavelength), ``pairing`` ("split_half", the
+    default, or "interleaved": the checkpoint pairs entry 2i with 2i + 1, and the mixer lays the rows of its q and k
+    projections out by ``permutation()`` when it loads them, after which the split-half kernels apply).  The part
     holds the table (``inv_freq``, float32) and the magnitude; the mixer that uses it rotates inside
     its own kernel between its norm and its cache write (``ops.normed_qk_store``)."""
 
@@ -87,10 +119,15 @@ class RotaryPartial(Positions):
         self.dims = int(spec.params["dims"])
         self.base = float(spec.params["base"])
         self.scaling = spec.params.get("scaling")
+        self.pairing = spec.params.get("pairing", "split_half")
         if self.dims % 2 or not 0 < self.dims <= self.head_dim:
             raise ValueError(f"{self.dims} rotated entries do not fit a head of {self.head_dim}")
         self.inv_freq = None
         self.magnitude = 1.0
+        pair_permutation(self.head_dim, self.dims, self.pairing)  # refuses an unknown pairing
+
+    def permutation(self) -> list:
+        return pair_permutation(self.head_dim, self.dims, self.pairing)
 
     def load(self, tensors: dict, prefix: str, device, dtype) -> None:
         freq, self.magnitude = scaled_frequencies(self.dims, self.base, self.scaling)

@@ -9,6 +9,11 @@ weight multiplies the expert's INPUT (``weight_on`` "input": out = sum_j expert_
 W_down,e (silu(W_gate,e h) * W_up,e h).  ``groups`` > 1 with ``keep`` < groups: the experts form ``groups``
 equal groups of neighbours, a group's score is its largest member's, and only experts of the ``keep`` best groups
 can be chosen.  With ``renormalize`` the chosen scores are divided by their sum + ``renorm_eps``.
+``correction``: a tensor of one number an expert is added to the scores for the CHOICE only (the weights stay the
+scores).  ``weight_scale`` multiplies the weights.  ``identity`` = n: the router has n more outputs than there are
+experts; the last n are identity experts without tensors, whose output is their input (times the weight).
+``shared``: a feed-forward part (with its prefix ``shared_prefix`` below this one's) that runs for every token beside
+the routed experts and adds its own output.
 
 Routing, the expert-sorted order and the products are planned and run on the device (csrc/moe.cu):
 nothing is read back, so steps of single tokens are captured like any other part's.  In bfloat16 the
@@ -18,8 +23,9 @@ activation in its epilogue over gate and up rows interleaved by 16; in float32, 
 kernel does not take, on CUDA cores in tiles of 64 rows.
 
 Parameters: ``hidden_size``, ``intermediate_size``, ``limit``, ``alpha``, ``num_experts``, ``top_k``,
-``score``, ``renormalize``, ``renorm_eps``, ``weight_on``, ``groups``, ``keep``.  Tensors below the prefix: router [E, hidden];
-e<j>.gate, e<j>.up [ff, hidden]; e<j>.down [hidden, ff].
+``score``, ``renormalize``, ``renorm_eps``, ``weight_on``, ``groups``, ``keep``, ``correction``, ``weight_scale``,
+``identity``, ``shared``, ``shared_prefix``.  Tensors below the prefix: router [E + identity, hidden];
+e<j>.gate, e<j>.up [ff, hidden]; e<j>.down [hidden, ff]; correction [E + identity].
 """
 from __future__ import annotations
 
@@ -27,7 +33,7 @@ import torch
 
 from .. import ops
 from ..config.spec import PartSpec
-from .base import FEED_FORWARDS, FeedForward, TensorSpec
+from .base import FEED_FORWARDS, FeedForward, TensorSpec, build_part
 
 
 @FEED_FORWARDS.register("routed_clamped_glu")
@@ -51,16 +57,27 @@ class RoutedClampedGLU(FeedForward):
         self.keep = int(p.get("keep", self.groups))
         if self.groups < 1 or self.num_experts % self.groups or not 1 <= self.keep <= self.groups:
             raise ValueError(f"{self.num_experts} experts cannot form {self.groups} equal groups of which {self.keep} are kept")
-        if self.top_k > self.keep * (self.num_experts // self.groups):
+        if self.top_k > self.keep * ((self.num_experts + int(p.get("identity", 0) or 0)) // self.groups):
             raise ValueError(f"top_k {self.top_k} exceeds the {self.keep} kept groups' experts")
         if self.score not in ("sigmoid", "softmax"):
             raise ValueError(f"unknown router score {self.score!r} (known: sigmoid, softmax)")
         if self.weight_on not in ("input", "output"):
             raise ValueError(f"weight_on must be 'input' or 'output', got {self.weight_on!r}")
-        if not 0 < self.top_k <= self.num_experts:
+        if not 0 < self.top_k <= self.num_experts + int(p.get("identity", 0) or 0):
             raise ValueError(f"top_k {self.top_k} does not fit {self.num_experts} experts")
-        if self.num_experts > 256:
+        self.identity = int(p.get("identity", 0) or 0)
+        self.router_outputs = self.num_experts + self.identity
+        self.has_correction = bool(p.get("correction", False))
+        self.weight_scale = float(p.get("weight_scale", 1.0))
+        if self.router_outputs > 256:
             raise ValueError("the router kernel takes up to 256 experts")
+        if self.identity and (self.weight_on != "output" or self.groups != 1):
+            raise ValueError("identity experts are built with the weight on the output and without groups")
+        if self.top_k > self.router_outputs:
+            raise ValueError(f"top_k {self.top_k} does not fit {self.router_outputs} router outputs")
+        self.shared = build_part(FEED_FORWARDS, p["shared"]) if p.get("shared") is not None else None
+        self.shared_prefix = str(p.get("shared_prefix", "shared."))
+        self.correction = None
         self.router = self.gate_up = self.down = None
         self.tensor_cores = False
 
@@ -72,12 +89,21 @@ class RoutedClampedGLU(FeedForward):
         for e in range(experts):
             out += [TensorSpec(f"{prefix}e{e}.gate", (inter, hidden)), TensorSpec(f"{prefix}e{e}.up", (inter, hidden)),
                     TensorSpec(f"{prefix}e{e}.down", (hidden, inter))]
-        out.append(TensorSpec(prefix + "router", (experts, hidden)))
+        outputs = experts + int(p.get("identity", 0) or 0)
+        out.append(TensorSpec(prefix + "router", (outputs, hidden)))
+        if p.get("correction", False):
+            out.append(TensorSpec(prefix + "correction", (outputs,), init="zeros"))
+        if p.get("shared") is not None:
+            out += FEED_FORWARDS.get(p["shared"].kind).expected_tensors(p["shared"], prefix + str(p.get("shared_prefix", "shared.")))
         return out
 
     def load(self, tensors: dict, prefix: str, device, dtype) -> None:
         E = self.num_experts
         self.router = tensors[prefix + "router"].to(device=device, dtype=torch.float32).contiguous()
+        if self.has_correction:
+            self.correction = tensors[prefix + "correction"].to(device=device, dtype=torch.float32).contiguous()
+        if self.shared is not None:
+            self.shared.load(tensors, prefix + self.shared_prefix, device, dtype)
         from . import swiglu_bf16
 
         # per expert [gate; up] stacked, [E, 2 ff, hidden], and [E, hidden, ff]; for the tensor-core product the
@@ -121,7 +147,7 @@ class RoutedClampedGLU(FeedForward):
         y = ctx.buffer("moe.y", (most_rows, self.hidden_size), torch.float32)[:rows]
         on_input = self.weight_on == "input"
         ops.moe_route(x, self.router, choice, weight, self.score == "softmax", self.renormalize, self.groups, self.keep,
-                      self.renorm_eps)
+                      self.renorm_eps, correction=self.correction, scale=self.weight_scale)
         ops.moe_plan(choice, position, plan, E, tile)
         ops.moe_scatter(x, position, weight, sorted_x, top, weighted=on_input)
         if self.tensor_cores:
@@ -131,4 +157,6 @@ class RoutedClampedGLU(FeedForward):
         else:
             ops.moe_gemm_simt(sorted_x, self.gate_up, act, plan, glu=True, limit=self.limit, alpha=self.alpha)
             ops.moe_gemm_simt(act, self.down, y, plan)
-        ops.moe_combine(y, position, weight, acc, top, weighted=not on_input)
+        ops.moe_combine(y, position, weight, acc, top, weighted=not on_input, x=x if self.identity else None)
+        if self.shared is not None:
+            self.shared.forward(ctx, x, acc)
