@@ -424,14 +424,15 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     parser.add_argument("--skip-points", action="store_true", help="leave out prefill, batch 1/64 and e2e")
     parser.add_argument("--workload", choices=["interleave14b", "stress05b", "dodonex", "dodonex-1b", "numuzen", "numuzen-1b", "fusolix",
-                                               "fusolix-1b"],
+                                               "fusolix-1b", "kilatar", "kilatar-1b"],
                         default=None,
                         help="instead of the headline line: the mixed step at Qwen2.5-14B layer sizes, 256 requests "
                              "arriving at Qwen2.5-0.5B layer sizes (torchlet_b200/benchmarks/workloads.py), or prefill and "
                              "decode of the Dodonex design beside a Qwen2 model of equal size "
                              "(torchlet_b200/benchmarks/dodonex.py), or the same of the Numuzen design beside a Dodonex and "
                              "a Qwen2 model of equal size (torchlet_b200/benchmarks/numuzen.py), or the same of the Fusolix design "
-                             "beside a Numuzen model of equal size (torchlet_b200/benchmarks/fusolix.py)")
+                             "beside a Numuzen model of equal size (torchlet_b200/benchmarks/fusolix.py), or the same of the Kilatar "
+                             "design beside a Fusolix model of equal size (torchlet_b200/benchmarks/kilatar.py)")
     args = parser.parse_args()
     if args.gpus != 1:
         print("bench.py: this engine runs on one GPU only; --gpus must be 1")
@@ -442,7 +443,12 @@ def main() -> int:
         from torchlet_b200.benchmarks import workloads
 
         peaks, peak_source = load_peaks()
-        if args.workload.startswith("fusolix"):
+        if args.workload.startswith("kilatar"):
+            from torchlet_b200.benchmarks import kilatar
+
+            record = kilatar.run(size="1b" if args.workload.endswith("1b") else "2b", layers=args.layers or 8,
+                                 batch=args.batch, context=min(args.context, 2048), kernels=True)
+        elif args.workload.startswith("fusolix"):
             from torchlet_b200.benchmarks import fusolix
 
             record = fusolix.run(size="1b" if args.workload.endswith("1b") else "2b", layers=args.layers or 8,

@@ -19,8 +19,8 @@ product with float32 output, because norm and rotation are float32; one kernel t
 and writes q and the cache rows (csrc/gated_attention.cu), and the paged attention kernels of the
 plain attention mixer do the rest with softcap, sink and gate as arguments.
 
-Heads whose key and value sizes differ (or are no multiple of 8) are laid out at load time in rows of one padded size
-P: zero rows in W_q, W_k and W_v, zero columns in W_o, so that scores and outputs are what they were and every paged
+Heads whose key and value sizes differ are laid out at load time in rows of one padded size P (the larger of the two,
+rounded up to a multiple of 8): zero rows in W_q, W_k and W_v, zero columns in W_o, so that scores and outputs are what they were and every paged
 kernel sees heads of P entries.  A position part with ``pairing`` "interleaved" has the rows of W_q and W_k laid out
 by its ``permutation()`` in the same pass.
 
@@ -52,8 +52,9 @@ class GatedAttentionMixer(Mixer):
         self.num_kv_heads = int(p["num_kv_heads"])
         self.qk_dim = int(p["head_dim"])
         self.v_dim = int(p["v_dim"]) if p.get("v_dim") is not None else self.qk_dim
-        # the size of a head as the kernels and the pages see it
-        self.head_dim = self.qk_dim if self.v_dim == self.qk_dim and self.qk_dim % 8 == 0 else -(-max(self.qk_dim, self.v_dim) // 8) * 8
+        # the size of a head as the kernels and the pages see it: the larger of the two where they differ (then rounded up
+        # to a multiple of 8, which the kernels' 16-byte loads want)
+        self.head_dim = self.qk_dim if self.v_dim == self.qk_dim else -(-max(self.qk_dim, self.v_dim) // 8) * 8
         self.padded = self.head_dim != self.qk_dim or self.head_dim != self.v_dim
         self.scale = float(p["scale"]) if p.get("scale") is not None else self.qk_dim ** -0.5
         self.softcap: Optional[float] = float(p["softcap"]) if p.get("softcap") else None
@@ -76,8 +77,8 @@ class GatedAttentionMixer(Mixer):
         if self.head_dim > 256:
             raise ValueError(f"head_dim {self.head_dim} is not supported (up to 256)")
         if self.padded and (self.qk_norm is not None or self.values_from_keys):
-            raise ValueError("heads whose key and value sizes differ (or are no multiple of 8) are not built together "
-                             "with a norm over the whole projection or with values taken from the keys")
+            raise ValueError("heads whose key and value sizes differ are not built together with a norm over the whole "
+                             "projection or with values taken from the keys")
         self.positions = build_part(POSITIONS, p["positions"]) if p.get("positions") else None
         if self.positions is not None and not hasattr(self.positions, "inv_freq"):
             raise ValueError("this mixer rotates inside its own kernel and needs a position part with a frequency table")
