@@ -95,6 +95,16 @@ CASES = {
               parallel(chunked(4, 2, 128, 128, 0.09, 150, rot(50000.0, 128)), lightning(1, 128, 32, (0.98,)), moe(4, 2, 64)),
               mamba(4, 32, 64, 2, 4, 4, None),
           ]},
+    # sizes that are no multiple of 8 (the products' and the attention's any-size kernels in both engines), a chunk longer
+    # than every test sequence, five taps, three norm groups, three of four router outputs of which two are identity
+    "S": {"architecture": "Kilatar", "vocab": 53, "width": 100, "norm": {"eps": 1e-5},
+          "loop": {"start": 2, "stop": 3, "times": 2},
+          "layers": [
+              mamba(3, 10, 6, 3, 5, 3, moe(2, 3, 20, identity=2, scale=0.8, shared=12)),
+              latent(2, 12, 6, 10, 20, 0.25, rot(300.0, 6), dense(36)),
+              parallel(chunked(5, 5, 12, 12, 0.3, 1000, rot(300.0, 4, (2.0, 1.0, 3.0, 16))),
+                       lightning(2, 10, 14, (0.8, 0.95)), dense(28)),
+          ]},
 }
 
 

@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
 
 
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_whole_prompt_and_first_tokens(name, dtype):
     name = cases.variant(name, dtype)
@@ -61,7 +61,7 @@ def test_prefill_then_token_by_token(name, dtype):
     cases.assert_close(got, want[:40], dtype, f"{name} token by token")
 
 
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("page_size", [8, 16])
 def test_portions_of_changing_size(name, dtype, page_size):
@@ -139,7 +139,7 @@ def test_unequal_batches_with_pages_and_slots_used_again(name, dtype):
         assert torch.equal(torch.cat(got[2]), alone)
 
 
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_captured_decode_step_with_padding_lanes(name, dtype):
     """Three requests decode together in a bucket of four lanes (one is padding) from the captured graph; the states of

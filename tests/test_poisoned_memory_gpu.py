@@ -14,6 +14,7 @@ pytestmark = pytest.mark.gpu
 
 
 def poison(total_mb: int) -> None:
+    torch.cuda.empty_cache()  # blocks that earlier tests left in the allocator would be handed out first, unpoisoned
     blocks, left, i = [], total_mb << 20, 0
     sizes = [1 << 12, 1 << 16, 1 << 20, 1 << 22, 1 << 24, 1 << 26]  # the allocator keeps small and large blocks apart
     while left > 0:

@@ -58,8 +58,11 @@ struct Params {
   // persistent kernel (normal orientation): tile width, stages, tile counts
   int block_q, stages, row_tiles, num_tiles;
   // the gated epilogue: limit 0: silu(gate) * up; limit > 0: g = min(gate, limit), u = clamp(up, +-limit),
-  // g * sigmoid(alpha g) * (u + 1)
+  // g * sigmoid(alpha g) * (u + 1); limit < 0: the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))) * up.
+  // ``bias`` (interleaved like the weight rows) is added to gate and up first; ``row_scale`` (one float32 number a
+  // token, or nullptr) multiplies the result before it is rounded.
   float glu_limit, glu_alpha;
+  const float* row_scale;
   // grouped product (persistent kernel): row tile i belongs to ONE group, plan[1 + i] (plan[0] tiles are in
   // use; a negative group or a tile past plan[0] is skipped); group g's weights are rows
   // [g group_rows, (g + 1) group_rows) of the column operand.  nullptr: one group.
@@ -74,6 +77,7 @@ __device__ __forceinline__ float gated(float g, float u, float limit, float alph
     u = fminf(fmaxf(u, -limit), limit);
     return g / (1.f + __expf(-alpha * g)) * (u + 1.f);
   }
+  if (limit < 0.f) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
   return silu(g) * u;
 }
 
@@ -85,10 +89,14 @@ __device__ __forceinline__ void epilogue_chunk(const Params& p, int m, int n0, c
     if (n0 + 32 > N) return;  // N is a multiple of 32 by construction of the interleave
     __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)m * p.ldo + (n0 >> 1);
     uint32_t packed[8];
+    const float scale = p.row_scale ? p.row_scale[m] : 1.f;
+    const float* bias = p.bias ? p.bias + n0 : nullptr;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float a = gated(v[2 * j], v[2 * j + 16], p.glu_limit, p.glu_alpha);
-      const float b = gated(v[2 * j + 1], v[2 * j + 17], p.glu_limit, p.glu_alpha);
+      const float g0 = v[2 * j] + (bias ? bias[2 * j] : 0.f), u0 = v[2 * j + 16] + (bias ? bias[2 * j + 16] : 0.f);
+      const float g1 = v[2 * j + 1] + (bias ? bias[2 * j + 1] : 0.f), u1 = v[2 * j + 17] + (bias ? bias[2 * j + 17] : 0.f);
+      const float a = gated(g0, u0, p.glu_limit, p.glu_alpha) * scale;
+      const float b = gated(g1, u1, p.glu_limit, p.glu_alpha) * scale;
       __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
       packed[j] = *reinterpret_cast<uint32_t*>(&h);
     }
@@ -359,12 +367,15 @@ gemm_tc_swapped_kernel(const __grid_constant__ CUtensorMap map_row, const __grid
       } else if (p.epilogue == EPI_SWIGLU_BF16) {
         // lanes 0-15 hold gate rows, lanes 16-31 the matching up rows (interleave of 16)
         const int out_col = ((row0 + quarter * 32) >> 1) + lane;
+        const float b = (p.bias && row < p.rows) ? p.bias[row] : 0.f;
 #pragma unroll
         for (int j = 0; j < CHUNK; ++j) {
-          const float up = __shfl_down_sync(0xffffffffu, v[j], 16);
+          const float mine = v[j] + b;
+          const float up = __shfl_down_sync(0xffffffffu, mine, 16);
           const int m = col0 + c + j;
           if (live && lane < 16 && m < p.cols)
-            ((__nv_bfloat16*)p.out)[(size_t)m * p.ldo + out_col] = __float2bfloat16_rn(gated(v[j], up, p.glu_limit, p.glu_alpha));
+            ((__nv_bfloat16*)p.out)[(size_t)m * p.ldo + out_col] =
+                __float2bfloat16_rn(gated(mine, up, p.glu_limit, p.glu_alpha) * (p.row_scale ? p.row_scale[m] : 1.f));
         }
       } else if (live) {
         const float b = p.bias ? p.bias[row] : 0.f;
@@ -739,7 +750,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_co
 // Adds the split partials [splits][M][N] in ascending split order and applies the epilogue.
 __global__ void splitk_finish_kernel(const float* __restrict__ partial, int splits, int M, int N,
                                      const float* __restrict__ bias, int epilogue, void* out, long long ldo,
-                                     float glu_limit, float glu_alpha) {
+                                     float glu_limit, float glu_alpha, const float* __restrict__ row_scale) {
   tl::pdl_wait();               // everything before us in the stream is complete and visible
   tl::pdl_launch_dependents();  // the next kernel may start its own prologue
 
@@ -755,7 +766,12 @@ __global__ void splitk_finish_kernel(const float* __restrict__ partial, int spli
       gate += partial[s * plane + (size_t)m * N + g];
       up += partial[s * plane + (size_t)m * N + g + 16];
     }
-    ((__nv_bfloat16*)out)[(size_t)m * ldo + c] = __float2bfloat16_rn(gated(gate, up, glu_limit, glu_alpha));
+    if (bias) {
+      gate += bias[g];
+      up += bias[g + 16];
+    }
+    ((__nv_bfloat16*)out)[(size_t)m * ldo + c] =
+        __float2bfloat16_rn(gated(gate, up, glu_limit, glu_alpha) * (row_scale ? row_scale[m] : 1.f));
     return;
   }
   float v = 0.f;
@@ -1021,7 +1037,8 @@ int tl_gemm_tc_error() {
 // [M, N/2], 3 float32 out.  workspace: float32 scratch of at least tl_gemm_tc_plan bytes.
 static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* out, long long ldo, int epilogue, int M,
                         int N, int K, long long ldx, long long ldw, void* workspace, long long workspace_bytes,
-                        int defer, int* splits_out, float glu_limit, float glu_alpha, cudaStream_t stream);
+                        int defer, int* splits_out, float glu_limit, float glu_alpha, cudaStream_t stream,
+                        const float* row_scale = nullptr);
 
 int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long long ldo, int epilogue, int M,
                int N, int K, long long ldx, long long ldw, void* workspace, long long workspace_bytes, int defer,
@@ -1040,12 +1057,24 @@ int tl_gemm_tc_glu(const void* x, const void* w, void* out, long long ldo, int M
                       nullptr, limit, alpha, stream);
 }
 
+// The gated epilogue (2) with a choice of activation (0 silu, 1 the tanh form of gelu), optional biases of gate and up
+// (float32 [N], interleaved by 16 like the rows of w) and an optional factor of one float32 number a token.
+int tl_gemm_tc_gated(const void* x, const void* w, const float* bias, const float* row_scale, void* out, long long ldo,
+                     int M, int N, int K, long long ldx, long long ldw, void* workspace, long long workspace_bytes,
+                     int activation, cudaStream_t stream) {
+  if (activation < 0 || activation > 1) return TL_ERR_UNSUPPORTED;
+  return gemm_tc_impl(x, w, bias, out, ldo, EPI_SWIGLU_BF16, M, N, K, ldx, ldw, workspace, workspace_bytes, 0, nullptr,
+                      activation == 1 ? -1.f : 0.f, 0.f, stream, row_scale);
+}
+
 static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* out, long long ldo, int epilogue, int M,
                         int N, int K, long long ldx, long long ldw, void* workspace, long long workspace_bytes,
-                        int defer, int* splits_out, float glu_limit, float glu_alpha, cudaStream_t stream) {
+                        int defer, int* splits_out, float glu_limit, float glu_alpha, cudaStream_t stream,
+                        const float* row_scale) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || epilogue < 0 || epilogue > 3) return TL_ERR_UNSUPPORTED;
-  if (epilogue == EPI_SWIGLU_BF16 && (N % 32 || bias)) return TL_ERR_UNSUPPORTED;
+  if (epilogue == EPI_SWIGLU_BF16 && N % 32) return TL_ERR_UNSUPPORTED;
+  if (epilogue != EPI_SWIGLU_BF16 && row_scale) return TL_ERR_UNSUPPORTED;
   const Plan plan = make_plan(M, N, K);
   Params p;
   p.k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
@@ -1059,6 +1088,7 @@ static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* o
   p.ahead = 8;  // all stages
   p.glu_limit = glu_limit;
   p.glu_alpha = glu_alpha;
+  p.row_scale = row_scale;
   p.plan = nullptr;
   p.group_rows = 0;
   if (splits_out) *splits_out = 0;
@@ -1097,7 +1127,7 @@ static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* o
     const int out_cols = epilogue == EPI_SWIGLU_BF16 ? N / 2 : N;
     const long long total = (long long)M * out_cols;
     tl::launch_kernel(splitk_finish_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, p.partial, plan.splits, M, N, bias,
-                                                                             epilogue, out, ldo, glu_limit, glu_alpha);
+                                                                             epilogue, out, ldo, glu_limit, glu_alpha, row_scale);
     return TL_LAUNCH_CHECK();
   }
   p.rows = M;
@@ -1147,7 +1177,7 @@ static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* o
     const int out_cols = epilogue == EPI_SWIGLU_BF16 ? N / 2 : N;
     const long long total = (long long)M * out_cols;
     tl::launch_kernel(splitk_finish_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, p.partial, plan.splits, M, N,
-                      bias, epilogue, out, ldo, glu_limit, glu_alpha);
+                      bias, epilogue, out, ldo, glu_limit, glu_alpha, row_scale);
     return TL_LAUNCH_CHECK();
   }
   p.k_blocks_per_split = p.k_blocks;
@@ -1203,6 +1233,7 @@ int tl_gemm_tc_grouped(const void* x, const void* w, void* out, long long ldo, i
     p.ahead = 8;
     p.glu_limit = glu_limit;
     p.glu_alpha = glu_alpha;
+    p.row_scale = nullptr;
     p.plan = plan;
     p.group_rows = N;
     p.rows = N;     // weight rows of one group
@@ -1228,6 +1259,7 @@ int tl_gemm_tc_grouped(const void* x, const void* w, void* out, long long ldo, i
   p.ahead = 8;
   p.glu_limit = glu_limit;
   p.glu_alpha = glu_alpha;
+  p.row_scale = nullptr;
   p.plan = plan;
   p.group_rows = N;
   p.rows = rows;

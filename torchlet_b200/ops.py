@@ -55,6 +55,8 @@ _SIGNATURES = {
                        c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p],
         "tl_gemm_tc_glu": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p,
                            c_longlong, c_float, c_float, c_void_p],
+        "tl_gemm_tc_gated": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_longlong,
+                             c_longlong, c_void_p, c_longlong, c_int, c_void_p],
         "tl_gemm_tc_grouped": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                                c_float, c_float, c_void_p],
         "tl_gemm_tc_plan": [c_int, c_int, c_int, c_void_p, c_void_p],
@@ -1087,6 +1089,26 @@ def gemm_tc_glu(x, w, out, limit: float, alpha: float) -> None:
         x.data_ptr(), w.data_ptr(), out.data_ptr(), out.stride(0), M, N, K, x.stride(0), w.stride(0), _ptr(ws),
         ws.numel() * 4 if ws is not None else 0, float(limit), float(alpha), _stream())
     _check(code, "gemm_tc_glu", 2 if need and splits > 1 else 1)
+
+
+def gemm_tc_gated(x, w, out, activation: str = "silu", bias=None, row_scale=None) -> None:
+    """out = act(gate + b_gate) * (up + b_up) (* row_scale[token]), where gate and up are the 16-interleaved rows of
+    ``w`` applied to ``x``: the product, the biases, the activation ("silu" or "gelu_tanh") and the token's factor as
+    one kernel (the gated epilogue of csrc/gemm_tc.cu).  ``bias`` float32 [N], interleaved like the rows of ``w``;
+    ``row_scale`` float32 [M]; out bfloat16 [M, N / 2]."""
+    _need_cuda(x, w, out, bias, row_scale)
+    _release_workspace()
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.stride(1) == 1 and out.dtype == torch.bfloat16 and out.shape == (M, N // 2)
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == N and bias.is_contiguous())
+    assert row_scale is None or (row_scale.dtype == torch.float32 and row_scale.numel() == M and row_scale.is_contiguous())
+    need, _, splits = _gemm_plan(M, N, K)
+    ws = _workspace(x.device, need) if need else None
+    code = _fn("gemm_tc", "tl_gemm_tc_gated")(
+        x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(row_scale), out.data_ptr(), out.stride(0), M, N, K, x.stride(0),
+        w.stride(0), _ptr(ws), ws.numel() * 4 if ws is not None else 0, GLU_ACTIVATIONS[activation], _stream())
+    _check(code, "gemm_tc_gated", 2 if need and splits > 1 else 1)
 
 
 GROUPED_TILE_ROWS = 128  # rows of a tile of the grouped tcgen05 product: every group's rows are padded to these

@@ -6,8 +6,9 @@ With ``token_gate`` (the name of a [1, hidden] tensor below the prefix) the outp
 sigmoid(w_gate . x), one float32 number a token (an always-on expert beside routed ones); it is applied to the
 activated rows before the down product, which is the same number.
 
-In bfloat16 without biases and with silu the gate and up products are ONE tcgen05 product over 16-interleaved rows with
-the activation in its epilogue (as ``swiglu``); otherwise one product over [gate; up] and an activation kernel.
+In bfloat16 the gate and up products are ONE tcgen05 product over 16-interleaved rows with the biases, the activation
+and the token's gate in its epilogue (``ops.gemm_tc_gated``); in float32, and at sizes that kernel does not take, one
+product over [gate; up] and an activation kernel.
 
 Parameters: ``hidden_size``, ``intermediate_size``, ``activation`` ("silu", "gelu_tanh"), ``bias`` (default False),
 ``token_gate`` (default None), and the tensors' names below the prefix: ``gate_name``, ``up_name``, ``down_name``
@@ -39,6 +40,7 @@ class GatedMLP(FeedForward):
             raise ValueError("a gate of one number a token is not built together with biases")
         self.gate_up_proj: Linear | None = None
         self.gate_up_interleaved = None  # bfloat16 fused path: gate/up rows interleaved by 16
+        self.gate_up_bias = None  # ... and their biases in the same order
         self.down_proj: Linear | None = None
         self.token_gate_weight = None
 
@@ -66,11 +68,13 @@ class GatedMLP(FeedForward):
 
         gate, up, down = self._names(self.spec, prefix)
         suffix = self.spec.params.get("bias_suffix", ".b")
-        fused = (dtype == torch.bfloat16 and not self.bias and not self.token_gate and self.activation == "silu"
-                 and swiglu_bf16.usable(self.hidden_size, self.intermediate_size))
+        fused = dtype == torch.bfloat16 and swiglu_bf16.usable(self.hidden_size, self.intermediate_size)
         if fused:
             self.gate_up_interleaved = swiglu_bf16.interleave(
                 tensors[gate].to(device=device, dtype=dtype), tensors[up].to(device=device, dtype=dtype))
+            if self.bias:  # interleaved by 16 like the rows they belong to
+                both = [tensors[name + suffix].to(device=device, dtype=torch.float32).view(-1, swiglu_bf16.BLOCK) for name in (gate, up)]
+                self.gate_up_bias = torch.cat(both, dim=1).reshape(-1).contiguous()
         else:
             bias = torch.cat([tensors[gate + suffix].float(), tensors[up + suffix].float()]) if self.bias else None
             self.gate_up_proj = Linear(torch.cat([tensors[gate], tensors[up]], dim=0), bias, device, dtype)
@@ -86,7 +90,7 @@ class GatedMLP(FeedForward):
             ops.token_gate(x, self.token_gate_weight, row_scale)
         act = ctx.buffer("gated_mlp.act", (tokens, self.intermediate_size), ctx.dtype)
         if self.gate_up_interleaved is not None:
-            ops.gemm_tc(x, self.gate_up_interleaved, act, None, ops.EPI_SWIGLU_BF16)
+            ops.gemm_tc_gated(x, self.gate_up_interleaved, act, self.activation, self.gate_up_bias, row_scale)
         else:
             gate_up = ctx.buffer("gated_mlp.gate_up", (tokens, 2 * self.intermediate_size), ctx.dtype)
             self.gate_up_proj.forward(x, gate_up)
