@@ -222,7 +222,7 @@ constexpr int EXPAND_WARPS = 8;
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(EXPAND_WARPS * 32)
 latent_expand_o_kernel(const T* __restrict__ o_lat, const T* __restrict__ uv, T* __restrict__ out, int tokens,
-                       int heads, int vdim, int kv_rank) {
+                       int heads, int vdim, int kv_rank, const float* __restrict__ gate, int gate_stride) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
   extern __shared__ float latent[];  // TOKENS x kv_rank floats
@@ -258,7 +258,11 @@ latent_expand_o_kernel(const T* __restrict__ o_lat, const T* __restrict__ uv, T*
 #pragma unroll
     for (int tt = 0; tt < TOKENS; ++tt) {
       const float total = warp_sum(sum[tt]);
-      if (lane == 0 && tt < count) out[(size_t)(t0 + tt) * heads * vdim + (size_t)h * vdim + v] = from_float<T>(total);
+      if (lane == 0 && tt < count) {
+        // gate (optional, float32 rows [tokens, heads * vdim]): the output is multiplied by sigmoid(gate)
+        const float g = gate ? 1.f / (1.f + expf(-gate[(size_t)(t0 + tt) * gate_stride + (size_t)h * vdim + v])) : 1.f;
+        out[(size_t)(t0 + tt) * heads * vdim + (size_t)h * vdim + v] = from_float<T>(total * g);
+      }
     }
   }
 }
@@ -343,7 +347,7 @@ int tl_latent_attention(const void* q_abs, const void* pages, int dtype, const i
 }
 
 int tl_latent_expand_o(const void* o_lat, const void* uv, void* out, int dtype, int tokens, int heads, int vdim,
-                       int kv_rank, cudaStream_t stream) {
+                       int kv_rank, const float* gate, int gate_stride, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (heads > 65535 || kv_rank > 1024) return TL_ERR_UNSUPPORTED;
   const int chunks = (tokens + TOKENS - 1) / TOKENS;
@@ -353,7 +357,7 @@ int tl_latent_expand_o(const void* o_lat, const void* uv, void* out, int dtype, 
   const bool vec = kv_rank % 8 == 0;
 #define TL_EXPAND(T, VEC)                                                                                          \
   tl::launch_kernel(latent_expand_o_kernel<T, VEC>, grid, EXPAND_WARPS * 32, smem, stream, (const T*)o_lat,        \
-                    (const T*)uv, (T*)out, tokens, heads, vdim, kv_rank)
+                    (const T*)uv, (T*)out, tokens, heads, vdim, kv_rank, gate, gate_stride)
   if (dtype == TL_DTYPE_F32) {
     if (vec) TL_EXPAND(float, true); else TL_EXPAND(float, false);
   } else {

@@ -7,7 +7,8 @@
 //               exp(-exp(A_log) dt) of every head; writes the scan's rows [C (G N) | B (G N) | dt x (H V)], the
 //               activated x and the decays.  Inputs before a step's first token of a request come from the request's
 //               slot (the last taps - 1 raw inputs), zeros before the start of a sequence;
-//   conv_state  moves the last taps - 1 raw inputs of every request into its slot;
+//   conv_state  moves the last taps - 1 raw inputs of every request into its slot (in a step of single tokens ``conv``
+//               does that itself);
 //   gated_norm  out = norm(y) * w with y = o (+ D_h x) and a gate: either y * act(gate) before the norm, or the norm
 //               first and the gate behind it; the norm is an RMS norm over ``groups`` equal parts of the row;
 //   activate    silu, in place, on the first columns of float32 rows;
@@ -34,10 +35,10 @@ __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log
 __global__ void __launch_bounds__(NT)
 ssm_conv_kernel(const float* __restrict__ proj, int proj_stride, int xbc_offset, int dt_offset,
                 const float* __restrict__ weight, const float* __restrict__ bias, const float* __restrict__ dt_bias,
-                const float* __restrict__ a_log, const float* __restrict__ state, const int* __restrict__ token_req,
+                const float* __restrict__ a_log, float* state, const int* __restrict__ token_req,
                 const int* __restrict__ req_indptr, const int* __restrict__ slots, float* __restrict__ scan_in,
                 float* __restrict__ x_out, float* __restrict__ decay, int channels, int taps, int heads, int vdim,
-                int gn, int max_slots) {
+                int gn, int max_slots, int update_state) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
   const int t = blockIdx.x;
@@ -56,12 +57,15 @@ ssm_conv_kernel(const float* __restrict__ proj, int proj_stride, int xbc_offset,
   float sum = bias[c];
   if (live) {
     const int i = t - req_indptr[req];  // the token's place in its request's portion
-    const float* old = state + (size_t)slot * (taps - 1) * channels;
+    float* old = state + (size_t)slot * (taps - 1) * channels;
     for (int j = 0; j < taps; ++j) {  // ascending j: oldest input first
       const int back = taps - 1 - j;
       const float v = i - back >= 0 ? proj[(size_t)(t - back) * proj_stride + xbc_offset + c]
                                     : old[(size_t)(taps - 1 + i - back) * channels + c];
       sum = fmaf(weight[(size_t)c * taps + j], v, sum);
+      // a step of single tokens: this thread alone reads and writes the channel's rows of the slot, so it also moves
+      // them up by one (row j - 1 takes the value just read from row j; the last row takes the token's own input)
+      if (update_state && j > 0) old[(size_t)(j - 1) * channels + c] = v;
     }
   }
   const float act = live ? silu_f(sum) : 0.f;
@@ -179,14 +183,14 @@ extern "C" {
 int tl_ssm_conv(const float* proj, int proj_stride, int xbc_offset, int dt_offset, const float* weight, const float* bias,
                 const float* dt_bias, const float* a_log, const float* state, const int* token_req,
                 const int* req_indptr, const int* slots, float* scan_in, float* x_out, float* decay, int tokens,
-                int taps, int heads, int vdim, int gn, int max_slots, cudaStream_t stream) {
+                int taps, int heads, int vdim, int gn, int max_slots, int update_state, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (taps < 1 || taps > MAX_TAPS || heads <= 0 || heads > NT || vdim <= 0 || gn <= 0) return TL_ERR_UNSUPPORTED;
   const int channels = heads * vdim + 2 * gn;
   dim3 grid(tokens, (channels + NT - 1) / NT);
   tl::launch_kernel(ssm_conv_kernel, grid, NT, 0, stream, proj, proj_stride, xbc_offset, dt_offset, weight, bias, dt_bias,
-                    a_log, state, token_req, req_indptr, slots, scan_in, x_out, decay, channels, taps, heads, vdim, gn,
-                    max_slots);
+                    a_log, (float*)state, token_req, req_indptr, slots, scan_in, x_out, decay, channels, taps, heads, vdim, gn,
+                    max_slots, update_state);
   return TL_LAUNCH_CHECK();
 }
 

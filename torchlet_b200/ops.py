@@ -128,7 +128,7 @@ _SIGNATURES = {
                                c_int, c_int, c_int, c_int, c_int, c_void_p],
         "tl_latent_attention": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                 c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
-        "tl_latent_expand_o": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "tl_latent_expand_o": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
         "tl_latent_attention_debug_error": [c_void_p],
     },
     "latent_attention_mma": {
@@ -166,7 +166,8 @@ _SIGNATURES = {
     },
     "ssm": {
         "tl_ssm_conv": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                        c_void_p],
         "tl_ssm_conv_state": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "tl_gated_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                           c_int, c_int, c_int, c_float, c_void_p],
@@ -735,12 +736,13 @@ def glu_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu", 
 
 
 def ssm_conv(proj, xbc_offset: int, dt_offset: int, weight, bias, dt_bias, a_log, state, token_req, req_indptr, slots,
-             scan_in, x_out, decay, heads: int, vdim: int, gn: int) -> None:
+             scan_in, x_out, decay, heads: int, vdim: int, gn: int, update_state: bool = False) -> None:
     """The front of a selective state-space mixer (csrc/ssm.cu): causal convolution over time of the channels
     proj[:, xbc_offset:] = [x (H V) | B (G N) | C (G N)] with ``weight`` [channels, taps] (last column: the current
     token) and ``bias``, silu; dt = softplus(proj[:, dt_offset:] + dt_bias); writes the scan's rows
     ``scan_in`` [C | B | dt x], ``x_out`` and ``decay`` [tokens, H] = exp(-exp(a_log) dt).  ``state`` [slots, taps - 1,
-    channels] holds each request's last raw inputs (None when taps == 1)."""
+    channels] holds each request's last raw inputs (None when taps == 1).  ``update_state``: every request brings ONE
+    token, and the kernel also moves that token's raw inputs into the slot's rows (else ``ssm_conv_state`` does)."""
     _need_cuda(proj, weight, bias, dt_bias, a_log, state, token_req, req_indptr, slots, scan_in, x_out, decay)
     tokens = proj.shape[0]
     channels, taps = weight.shape
@@ -752,7 +754,7 @@ def ssm_conv(proj, xbc_offset: int, dt_offset: int, weight, bias, dt_bias, a_log
                                      dt_bias.data_ptr(), a_log.data_ptr(), _ptr(state), token_req.data_ptr(),
                                      req_indptr.data_ptr(), slots.data_ptr(), scan_in.data_ptr(), x_out.data_ptr(),
                                      decay.data_ptr(), tokens, taps, heads, vdim, gn, state.shape[0] if state is not None else 0,
-                                     _stream())
+                                     1 if update_state else 0, _stream())
     _check(code, "ssm_conv")
 
 
@@ -960,14 +962,17 @@ def latent_attention_mma(q_abs, pages, block_table, req_indptr, kv_before, tile_
     _check(code, "latent_attention_mma", 2 if splits > 1 else 1)
 
 
-def latent_expand_o(o_lat, uv, out, heads, vdim, kv_rank) -> None:
-    """out[t, h] = W_uv,h o_lat[t, h];  uv [H vdim, kv_rank], out [T, H vdim]."""
-    _need_cuda(o_lat, uv, out)
+def latent_expand_o(o_lat, uv, out, heads, vdim, kv_rank, gate=None) -> None:
+    """out[t, h] = W_uv,h o_lat[t, h] (* sigmoid(gate[t, h]));  uv [H vdim, kv_rank], out [T, H vdim]; ``gate``: float32
+    rows (a view) of out's shape."""
+    _need_cuda(o_lat, uv, out, gate)
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape == out.shape)
     tokens = out.shape[0]
     assert o_lat.dtype == uv.dtype == out.dtype and o_lat.is_contiguous() and uv.is_contiguous() and out.is_contiguous()
     assert uv.shape == (heads * vdim, kv_rank) and out.shape == (tokens, heads * vdim)
     code = _fn("latent_attention", "tl_latent_expand_o")(o_lat.data_ptr(), uv.data_ptr(), out.data_ptr(),
-                                                         dtype_code(out.dtype), tokens, heads, vdim, kv_rank, _stream())
+                                                         dtype_code(out.dtype), tokens, heads, vdim, kv_rank, _ptr(gate),
+                                                         gate.stride(0) if gate is not None else 0, _stream())
     _check(code, "latent_expand_o")
 
 

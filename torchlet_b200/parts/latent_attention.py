@@ -220,8 +220,9 @@ class LatentAttentionMixer(Mixer):
                 ops.gemm_tc(o_lat[:, h * rank:(h + 1) * rank], self.uv[h * V:(h + 1) * V], out[:, h * V:(h + 1) * V],
                             None, ops.EPI_STORE_BF16)
         else:
-            ops.latent_expand_o(o_lat, self.uv, out, H, self.v_dim, self.kv_rank)
-        if self.gate:
+            ops.latent_expand_o(o_lat, self.uv, out, H, self.v_dim, self.kv_rank,
+                                gate=down[:, self.gate_offset:] if self.gate else None)
+        if self.gate and per_head_products:
             ops.gate_mul_(out, down[:, self.gate_offset:])
         if not self.o_proj.accumulate_later(ctx, out, acc):
             self.o_proj.forward(out, acc, accumulate=True)

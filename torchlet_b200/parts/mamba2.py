@@ -94,8 +94,9 @@ class Mamba2(Mixer):
         decay = ctx.buffer("mamba2.decay", (tokens, H), torch.float32)
         conv_state = cache.state.get("conv") if self.taps > 1 else None
         ops.ssm_conv(proj, inner, 2 * inner + 2 * gn, self.conv, self.conv_bias, self.dt_bias, self.a_log, conv_state,
-                     ctx.token_req, ctx.req_indptr, ctx.slots, scan_in, xs, decay, H, V, gn)
-        if conv_state is not None:
+                     ctx.token_req, ctx.req_indptr, ctx.slots, scan_in, xs, decay, H, V, gn,
+                     update_state=ctx.decode_only and conv_state is not None)
+        if conv_state is not None and not ctx.decode_only:
             ops.ssm_conv_state(proj, inner, conv_state, ctx.req_indptr, ctx.slots, ctx.num_requests)
         o = ctx.buffer("mamba2.o", (tokens, inner), torch.float32)
         ops.gla_scan(scan_in, decay, ctx.req_indptr, ctx.slots, cache.state["ssm"], o, ctx.num_requests, H, N, V, 1.0,
