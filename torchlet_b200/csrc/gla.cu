@@ -104,9 +104,12 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
   tl::pdl_wait();
   constexpr bool FIXED = MODE != DECAY_ROWS;  // no decay row is staged
   constexpr int PER = DK / KS;
-  constexpr int CHUNK = DK <= 64 ? 8 : (DK <= 128 ? 4 : 2);
-  __shared__ __align__(16) float stage[STAGES * CHUNK * (3 * DK + COLS + 4)];  // [STAGES][CHUNK]: q, k, a, v, token's decay
-  constexpr int row = 3 * DK + COLS + 4;
+  // a staged token: q, k, (a: only where the decay is a row a token), v, the token's decay number.  Without the a
+  // row a stage holds twice as many tokens of the larger key sizes, and the walk meets half as many barriers.
+  constexpr int VOFF = (FIXED ? 2 : 3) * DK;
+  constexpr int CHUNK = FIXED ? (DK <= 128 ? 8 : 4) : (DK <= 64 ? 8 : (DK <= 128 ? 4 : 2));
+  constexpr int row = VOFF + COLS + 4;
+  __shared__ __align__(16) float stage[STAGES * CHUNK * row];  // [STAGES][CHUNK]
   constexpr int NT = KS * COLS;
   const int req = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
   const int col0 = blockIdx.z * COLS;  // this block's value channels: col0 .. col0 + COLS
@@ -145,12 +148,12 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
           src = decay + (size_t)t * heads * dim + h * dim + 4 * q4;
           to = dst + tt * row + 2 * DK + 4 * q4;
         } else if (MODE == DECAY_TOKEN && rest == per_token - 1) {
-          copy4(dst + tt * row + 3 * DK + COLS, decay + (size_t)t * heads + h);
+          copy4(dst + tt * row + VOFF + COLS, decay + (size_t)t * heads + h);
           continue;
         } else {
           const int q4 = rest - (FIXED ? 2 : 3) * qd;
           src = proj + (size_t)t * proj_stride + 2 * hd + h * vdim + col0 + 4 * q4;
-          to = dst + tt * row + 3 * DK + 4 * q4;
+          to = dst + tt * row + VOFF + 4 * q4;
         }
         copy16(to, src);
       }
@@ -171,11 +174,11 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
           to = dst + tt * row + 2 * DK + i;
         } else if (MODE == DECAY_TOKEN && rest == per_token - 1) {
           src = decay + (size_t)t * heads + h;
-          to = dst + tt * row + 3 * DK + COLS;
+          to = dst + tt * row + VOFF + COLS;
         } else {
           const int i = rest - (FIXED ? 2 : 3) * dim;
           src = proj + (size_t)t * proj_stride + 2 * hd + h * vdim + col0 + i;
-          to = dst + tt * row + 3 * DK + i;
+          to = dst + tt * row + VOFF + i;
         }
         copy4(to, src);
       }
@@ -211,8 +214,8 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
       const float4* q4 = reinterpret_cast<const float4*>(tok);
       const float4* k4 = reinterpret_cast<const float4*>(tok + DK);
       const float4* a4 = reinterpret_cast<const float4*>(tok + 2 * DK);
-      const float v = tok[3 * DK + (on ? col - col0 : 0)];
-      const float fixed = MODE == DECAY_TOKEN ? tok[3 * DK + COLS] : head_decay;
+      const float v = tok[VOFF + (on ? col - col0 : 0)];
+      const float fixed = MODE == DECAY_TOKEN ? tok[VOFF + COLS] : head_decay;
       float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
       for (int n = 0; n < PER / 4; ++n) {

@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ router, int* __restrict__ choice,
                  float* __restrict__ weight, int tokens, int hidden, int experts, int top, int softmax_scores,
                  int renormalize, int groups, int keep, float renorm_eps, const float* __restrict__ correction,
-                 float scale) {
+                 float scale, const float* __restrict__ gate_w, float* __restrict__ gate_out) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
   extern __shared__ float xrow[];  // hidden floats
@@ -147,6 +147,11 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ rou
   for (int e = warp; e < experts; e += ROUTE_WARPS) {
     const float part = router_logit(xrow, router + (size_t)e * hidden, hidden, lane);
     if (lane == 0) all_scores[e] = part;
+  }
+  // a gate of one number a token beside the router (an always-on expert's): sigmoid(gate_w . x), by the last warp
+  if (gate_w && warp == ROUTE_WARPS - 1) {
+    const float z = router_logit(xrow, gate_w, hidden, lane);
+    if (lane == 0) gate_out[t] = 1.f / (1.f + expf(-z));
   }
   __syncthreads();
   if (warp != 0) return;
@@ -349,9 +354,11 @@ int tl_moe_tile_rows() { return BM; }
 
 // choice int32 [tokens, top], weight float32 [tokens, top]; router float32 [experts, hidden].
 // correction (optional, float32 [experts]): added to the scores for the choice only.  scale: multiplies the weights.
+// gate_w (optional, float32 [hidden]) with gate_out (float32 [tokens]): gate_out[t] = sigmoid(gate_w . x[t]).
 int tl_moe_route(const void* x, int ldx, int dtype, const float* router, int* choice, float* weight, int tokens,
                  int hidden, int experts, int top, int softmax_scores, int renormalize, int groups, int keep,
-                 float renorm_eps, const float* correction, float scale, cudaStream_t stream) {
+                 float renorm_eps, const float* correction, float scale, const float* gate_w, float* gate_out,
+                 cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (experts <= 0 || experts > MAX_EXPERTS || top <= 0 || top > experts) return TL_ERR_UNSUPPORTED;
   if (groups < 1 || keep < 1 || keep > groups || experts % groups || top > keep * (experts / groups) || groups > 2048)
@@ -362,11 +369,11 @@ int tl_moe_route(const void* x, int ldx, int dtype, const float* router, int* ch
   if (dtype == TL_DTYPE_F32)
     tl::launch_kernel(moe_route_kernel<float>, blocks, ROUTE_WARPS * 32, smem, stream, (const float*)x, ldx, router, choice,
                       weight, tokens, hidden, experts, top, softmax_scores, renormalize, groups, keep, renorm_eps, correction,
-                      scale);
+                      scale, gate_w, gate_out);
   else
     tl::launch_kernel(moe_route_kernel<__nv_bfloat16>, blocks, ROUTE_WARPS * 32, smem, stream, (const __nv_bfloat16*)x,
                       ldx, router, choice, weight, tokens, hidden, experts, top, softmax_scores, renormalize, groups, keep,
-                      renorm_eps, correction, scale);
+                      renorm_eps, correction, scale, gate_w, gate_out);
   return TL_LAUNCH_CHECK();
 }
 

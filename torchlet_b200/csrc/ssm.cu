@@ -104,56 +104,101 @@ ssm_conv_state_kernel(const float* __restrict__ proj, int proj_stride, int xbc_o
 
 // grid (tokens, groups).  y = o + skip[h] x (skip, x optional); gate_first: y *= act(gate), then the norm and the weight;
 // else the norm and the weight, then *= act(gate).  gate_act: 0 silu, 1 sigmoid.  The gate is float32 rows.
-template <typename T>
+// CACHED: the part's values (and, where the gate comes last, its factors) are kept in shared memory between the sum of
+// squares and the output, so memory is read once; every thread has four elements' loads in flight at a time.  Parts too
+// long for shared memory are read twice.
+template <typename T, bool CACHED>
 __global__ void __launch_bounds__(NT)
 gated_norm_kernel(const float* __restrict__ o, const float* __restrict__ x, const float* __restrict__ skip,
                   const float* __restrict__ gate, int gate_stride, const float* __restrict__ weight,
                   T* __restrict__ out, int width, int groups, int vdim, int gate_first, int gate_act, float eps) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
+  extern __shared__ float kept[];  // CACHED: part values, then (gate last) part factors
   __shared__ float scratch[32];
   const int t = blockIdx.x, part = width / groups, c0 = blockIdx.y * part;
   const float* row = o + (size_t)t * width;
+  const float* xr = x ? x + (size_t)t * width : nullptr;
   const float* g = gate + (size_t)t * gate_stride;
-  auto value = [&](int c) {
-    float y = row[c];
-    if (skip) y = fmaf(skip[c / vdim], x[(size_t)t * width + c], y);
-    if (gate_first) y *= gate_act ? sigmoid_f(g[c]) : silu_f(g[c]);
-    return y;
-  };
+  float* factor = kept + part;
   float ss = 0.f;
-  for (int c = c0 + threadIdx.x; c < c0 + part; c += NT) {
-    const float y = value(c);
-    ss = fmaf(y, y, ss);
+  for (int base = threadIdx.x; base < part; base += 4 * NT) {
+    float y[4], gv[4], xv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {  // the loads of four elements first
+      const int i = base + u * NT;
+      const bool in = i < part;
+      y[u] = in ? row[c0 + i] : 0.f;
+      gv[u] = in ? g[c0 + i] : 0.f;
+      xv[u] = (in && skip) ? xr[c0 + i] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = base + u * NT;
+      if (i >= part) break;
+      float v = skip ? fmaf(skip[(c0 + i) / vdim], xv[u], y[u]) : y[u];
+      const float a = gate_act ? sigmoid_f(gv[u]) : silu_f(gv[u]);
+      if (gate_first) v *= a;
+      ss = fmaf(v, v, ss);
+      if (CACHED) {
+        kept[i] = v;
+        if (!gate_first) factor[i] = a;
+      }
+    }
   }
-  ss = block_sum<NT>(ss, scratch);
+  ss = block_sum<NT>(ss, scratch);  // (its barriers also order the shared-memory writes before the reads below)
   const float inv = 1.f / sqrtf(ss / (float)part + eps);
-  for (int c = c0 + threadIdx.x; c < c0 + part; c += NT) {
-    float y = value(c) * inv * weight[c];
-    if (!gate_first) y *= gate_act ? sigmoid_f(g[c]) : silu_f(g[c]);
-    out[(size_t)t * width + c] = from_float<T>(y);
+  for (int i = threadIdx.x; i < part; i += NT) {
+    const int c = c0 + i;
+    float v, a = 1.f;
+    if (CACHED) {
+      v = kept[i];
+      if (!gate_first) a = factor[i];
+    } else {
+      v = skip ? fmaf(skip[c / vdim], xr[c], row[c]) : row[c];
+      const float ga = gate_act ? sigmoid_f(g[c]) : silu_f(g[c]);
+      if (gate_first) v *= ga; else a = ga;
+    }
+    out[(size_t)t * width + c] = from_float<T>(v * inv * weight[c] * a);
   }
 }
 
+// Four consecutive elements a thread where rows and columns allow 16-byte accesses, else one.
+template <bool VEC>
 __global__ void activate_kernel(float* __restrict__ rows, int stride, int cols, size_t total) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
-  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t e = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * (VEC ? 4 : 1);
   if (e >= total) return;
   float* at = rows + (e / cols) * stride + e % cols;
-  *at = silu_f(*at);
+  if (VEC) {
+    float4 v = *reinterpret_cast<float4*>(at);
+    v.x = silu_f(v.x); v.y = silu_f(v.y); v.z = silu_f(v.z); v.w = silu_f(v.w);
+    *reinterpret_cast<float4*>(at) = v;
+  } else {
+    *at = silu_f(*at);
+  }
 }
 
-template <typename T>
+template <typename T, bool VEC>
 __global__ void gate_mul_kernel(T* __restrict__ rows, const float* __restrict__ gate, int gate_stride, int cols,
                                 size_t total) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
-  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t e = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * (VEC ? 4 : 1);
   if (e >= total) return;
   const size_t t = e / cols;
   const int c = (int)(e % cols);
-  rows[e] = from_float<T>(to_float(rows[e]) * sigmoid_f(gate[t * gate_stride + c]));
+  if (VEC) {
+    const float4 g = *reinterpret_cast<const float4*>(gate + t * gate_stride + c);
+    T* at = rows + e;
+    at[0] = from_float<T>(to_float(at[0]) * sigmoid_f(g.x));
+    at[1] = from_float<T>(to_float(at[1]) * sigmoid_f(g.y));
+    at[2] = from_float<T>(to_float(at[2]) * sigmoid_f(g.z));
+    at[3] = from_float<T>(to_float(at[3]) * sigmoid_f(g.w));
+  } else {
+    rows[e] = from_float<T>(to_float(rows[e]) * sigmoid_f(gate[t * gate_stride + c]));
+  }
 }
 
 // One warp a token: out[t] = sigmoid(w . x[t]); each lane sums its 32nd in ascending k.
@@ -166,9 +211,16 @@ token_gate_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w,
   const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (t >= tokens) return;
   const T* row = x + (size_t)t * ldx;
-  float sum = 0.f;
-  for (int k = lane; k < hidden; k += 32) sum = fmaf(to_float(row[k]), w[k], sum);
-  sum = warp_sum(sum);
+  float p[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) p[i] = 0.f;
+  int k = lane;
+  for (; k + 224 < hidden; k += 256) {  // eight independent chains, eight loads in flight a lane
+#pragma unroll
+    for (int i = 0; i < 8; ++i) p[i] = fmaf(to_float(row[k + 32 * i]), w[k + 32 * i], p[i]);
+  }
+  for (; k < hidden; k += 32) p[0] = fmaf(to_float(row[k]), w[k], p[0]);
+  float sum = warp_sum(((p[0] + p[1]) + (p[2] + p[3])) + ((p[4] + p[5]) + (p[6] + p[7])));
   if (lane == 0) out[t] = sigmoid_f(sum);
 }
 
@@ -210,31 +262,43 @@ int tl_gated_norm(const float* o, const float* x, const float* skip, const float
   if (tokens <= 0) return 0;
   if (groups <= 0 || width % groups || groups > 65535 || vdim <= 0) return TL_ERR_UNSUPPORTED;
   dim3 grid(tokens, groups);
-  if (out_dtype == TL_DTYPE_F32)
-    tl::launch_kernel(gated_norm_kernel<float>, grid, NT, 0, stream, o, x, skip, gate, gate_stride, weight, (float*)out,
-                      width, groups, vdim, gate_first, gate_act, eps);
-  else
-    tl::launch_kernel(gated_norm_kernel<__nv_bfloat16>, grid, NT, 0, stream, o, x, skip, gate, gate_stride, weight,
-                      (__nv_bfloat16*)out, width, groups, vdim, gate_first, gate_act, eps);
+  const size_t smem = (size_t)(width / groups) * (gate_first ? 1 : 2) * sizeof(float);
+  const bool cached = smem <= 40 * 1024;
+#define TL_NORM(T, CACHED)                                                                                          \
+  tl::launch_kernel(gated_norm_kernel<T, CACHED>, grid, NT, CACHED ? smem : 0, stream, o, x, skip, gate, gate_stride, \
+                    weight, (T*)out, width, groups, vdim, gate_first, gate_act, eps)
+  if (out_dtype == TL_DTYPE_F32) {
+    if (cached) TL_NORM(float, true); else TL_NORM(float, false);
+  } else {
+    if (cached) TL_NORM(__nv_bfloat16, true); else TL_NORM(__nv_bfloat16, false);
+  }
+#undef TL_NORM
   return TL_LAUNCH_CHECK();
 }
 
 int tl_activate_silu(float* rows, int stride, int tokens, int cols, cudaStream_t stream) {
   const size_t total = (size_t)tokens * cols;
   if (total == 0) return 0;
-  tl::launch_kernel(activate_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, rows, stride, cols, total);
+  if (cols % 4 == 0 && stride % 4 == 0 && (reinterpret_cast<uintptr_t>(rows) & 15) == 0)
+    tl::launch_kernel(activate_kernel<true>, (unsigned)((total / 4 + 255) / 256), 256, 0, stream, rows, stride, cols, total);
+  else
+    tl::launch_kernel(activate_kernel<false>, (unsigned)((total + 255) / 256), 256, 0, stream, rows, stride, cols, total);
   return TL_LAUNCH_CHECK();
 }
 
 int tl_gate_mul(void* rows, int dtype, const float* gate, int gate_stride, int tokens, int cols, cudaStream_t stream) {
   const size_t total = (size_t)tokens * cols;
   if (total == 0) return 0;
-  const unsigned blocks = (unsigned)((total + 255) / 256);
-  if (dtype == TL_DTYPE_F32)
-    tl::launch_kernel(gate_mul_kernel<float>, blocks, 256, 0, stream, (float*)rows, gate, gate_stride, cols, total);
-  else
-    tl::launch_kernel(gate_mul_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)rows, gate, gate_stride,
-                      cols, total);
+  const bool vec = cols % 4 == 0 && gate_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(gate) & 15) == 0;
+  const unsigned blocks = (unsigned)(((vec ? total / 4 : total) + 255) / 256);
+#define TL_GATE(T, VEC) \
+  tl::launch_kernel(gate_mul_kernel<T, VEC>, blocks, 256, 0, stream, (T*)rows, gate, gate_stride, cols, total)
+  if (dtype == TL_DTYPE_F32) {
+    if (vec) TL_GATE(float, true); else TL_GATE(float, false);
+  } else {
+    if (vec) TL_GATE(__nv_bfloat16, true); else TL_GATE(__nv_bfloat16, false);
+  }
+#undef TL_GATE
   return TL_LAUNCH_CHECK();
 }
 

@@ -156,7 +156,7 @@ _SIGNATURES = {
     "moe": {
         "tl_moe_tile_rows": [],
         "tl_moe_route": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                         c_int, c_int, c_float, c_void_p, c_float, c_void_p],
+                         c_int, c_int, c_float, c_void_p, c_float, c_void_p, c_void_p, c_void_p],
         "tl_moe_plan": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "tl_moe_scatter": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "tl_moe_gemm_simt": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float,
@@ -818,13 +818,18 @@ def moe_tile_rows() -> int:
 
 
 def moe_route(x, router, choice, weight, softmax_scores: bool = False, renormalize: bool = False, groups: int = 1,
-              keep: int = 1, renorm_eps: float = 0.0, correction=None, scale: float = 1.0) -> None:
+              keep: int = 1, renorm_eps: float = 0.0, correction=None, scale: float = 1.0, token_gate=None) -> None:
     """choice[t, j], weight[t, j]: the ``top`` experts of every token by score (sigmoid or softmax of the
     float32 router logits) and their scores (csrc/moe.cu), divided by their sum + ``renorm_eps`` if
     ``renormalize``.  ``groups`` > 1: the experts form that many equal groups of neighbours and only experts of the
     ``keep`` groups with the largest best score can be chosen.  ``correction`` (float32 [experts]): the choice goes
-    by score + correction, the weights stay the scores.  ``scale`` multiplies the weights."""
-    _need_cuda(x, router, choice, weight, correction)
+    by score + correction, the weights stay the scores.  ``scale`` multiplies the weights.  ``token_gate`` (w float32
+    [hidden], out float32 [tokens]): the same kernel also writes out[t] = sigmoid(w . x[t]), the gate of an always-on
+    expert beside the routed ones."""
+    gate_w, gate_out = token_gate if token_gate is not None else (None, None)
+    _need_cuda(x, router, choice, weight, correction, gate_w, gate_out)
+    assert gate_w is None or (gate_w.dtype == gate_out.dtype == torch.float32 and gate_w.numel() == x.shape[1]
+                              and gate_out.numel() == x.shape[0] and gate_w.is_contiguous() and gate_out.is_contiguous())
     assert correction is None or (correction.dtype == torch.float32 and correction.numel() == router.shape[0])
     tokens, hidden = x.shape
     experts, top = router.shape[0], choice.shape[1]
@@ -833,7 +838,7 @@ def moe_route(x, router, choice, weight, softmax_scores: bool = False, renormali
     code = _fn("moe", "tl_moe_route")(x.data_ptr(), x.stride(0), dtype_code(x.dtype), router.data_ptr(), choice.data_ptr(),
                                       weight.data_ptr(), tokens, hidden, experts, top, 1 if softmax_scores else 0,
                                       1 if renormalize else 0, int(groups), int(keep), float(renorm_eps), _ptr(correction),
-                                      float(scale), _stream())
+                                      float(scale), _ptr(gate_w), _ptr(gate_out), _stream())
     _check(code, "moe_route")
 
 

@@ -82,10 +82,11 @@ class GatedMLP(FeedForward):
         if self.token_gate:
             self.token_gate_weight = tensors[prefix + self.token_gate].to(device=device, dtype=torch.float32).reshape(-1).contiguous()
 
-    def forward(self, ctx, x, acc) -> None:
+    def forward(self, ctx, x, acc, row_scale=None) -> None:
+        """``row_scale``: the token gate's numbers (float32 [tokens]) where the caller has computed them already (a router
+        whose kernel takes ``token_gate_weight`` along)."""
         tokens = x.shape[0]
-        row_scale = None
-        if self.token_gate_weight is not None:
+        if self.token_gate_weight is not None and row_scale is None:
             row_scale = ctx.buffer("gated_mlp.token_gate", (tokens,), torch.float32)
             ops.token_gate(x, self.token_gate_weight, row_scale)
         act = ctx.buffer("gated_mlp.act", (tokens, self.intermediate_size), ctx.dtype)

@@ -146,8 +146,12 @@ class RoutedClampedGLU(FeedForward):
         act = ctx.buffer("moe.act", (most_rows, self.intermediate_size), ctx.dtype)[:rows]
         y = ctx.buffer("moe.y", (most_rows, self.hidden_size), torch.float32)[:rows]
         on_input = self.weight_on == "input"
+        # a shared part with a gate of one number a token: the router's kernel has the token's row at hand and takes it along
+        gate_w = getattr(self.shared, "token_gate_weight", None)
+        shared_gate = ctx.buffer("moe.shared_gate", (tokens,), torch.float32) if gate_w is not None else None
         ops.moe_route(x, self.router, choice, weight, self.score == "softmax", self.renormalize, self.groups, self.keep,
-                      self.renorm_eps, correction=self.correction, scale=self.weight_scale)
+                      self.renorm_eps, correction=self.correction, scale=self.weight_scale,
+                      token_gate=(gate_w, shared_gate) if gate_w is not None else None)
         ops.moe_plan(choice, position, plan, E, tile)
         ops.moe_scatter(x, position, weight, sorted_x, top, weighted=on_input)
         if self.tensor_cores:
@@ -158,5 +162,7 @@ class RoutedClampedGLU(FeedForward):
             ops.moe_gemm_simt(sorted_x, self.gate_up, act, plan, glu=True, limit=self.limit, alpha=self.alpha)
             ops.moe_gemm_simt(act, self.down, y, plan)
         ops.moe_combine(y, position, weight, acc, top, weighted=not on_input, x=x if self.identity else None)
-        if self.shared is not None:
+        if self.shared is not None and shared_gate is not None:
+            self.shared.forward(ctx, x, acc, row_scale=shared_gate)
+        elif self.shared is not None:
             self.shared.forward(ctx, x, acc)
