@@ -31,53 +31,118 @@ __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); 
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
-// grid (tokens, ceil(channels / NT)).  channels = inner + 2 G N.
+// grid (ceil(tokens / CONV_TOKENS), ceil(channels / NT)).  channels = inner + 2 G N.  A thread takes one channel through
+// CONV_TOKENS consecutive tokens: its taps and bias stay in registers, and the last taps - 1 inputs slide along while the
+// tokens belong to one request (a request's tokens are consecutive in a step), so an input is loaded once; where a
+// request's portion begins inside the tile they are fetched anew, from the portion or from the request's slot.  The
+// step sizes of the block's heads are taken once a (token, head) into shared memory, not once a channel.
+constexpr int CONV_TOKENS = 8;
+
 __global__ void __launch_bounds__(NT)
 ssm_conv_kernel(const float* __restrict__ proj, int proj_stride, int xbc_offset, int dt_offset,
                 const float* __restrict__ weight, const float* __restrict__ bias, const float* __restrict__ dt_bias,
                 const float* __restrict__ a_log, float* state, const int* __restrict__ token_req,
                 const int* __restrict__ req_indptr, const int* __restrict__ slots, float* __restrict__ scan_in,
-                float* __restrict__ x_out, float* __restrict__ decay, int channels, int taps, int heads, int vdim,
-                int gn, int max_slots, int update_state) {
+                float* __restrict__ x_out, float* __restrict__ decay, int tokens, int channels, int taps, int heads,
+                int vdim, int gn, int max_slots, int update_state, int tile) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
-  const int t = blockIdx.x;
-  const int c = blockIdx.y * NT + threadIdx.x;
-  const int req = token_req[t];
-  const int slot = slots[req];
-  const bool live = TL_DEBUG_OK(slot >= -1 && slot < max_slots, TL_DEBUG_SLOT, slot) && slot >= 0;
+  __shared__ float step[CONV_TOKENS][NT + 1];  // dt of (token of the tile, head of the block)
+  __shared__ int tile_req[CONV_TOKENS], tile_slot[CONV_TOKENS], tile_place[CONV_TOKENS];
+  const int t0 = blockIdx.x * tile;  // ``tile`` tokens a block: CONV_TOKENS, or 1 where a step has few tokens
+  const int count = tokens - t0 < tile ? tokens - t0 : tile;
+  if (threadIdx.x < count) {  // the tokens' request, slot and place in their request's portion, once a block
+    const int req = token_req[t0 + threadIdx.x];
+    tile_req[threadIdx.x] = req;
+    tile_slot[threadIdx.x] = slots[req];
+    tile_place[threadIdx.x] = t0 + threadIdx.x - req_indptr[req];
+  }
+  const int c_lo = blockIdx.y * NT, c = c_lo + threadIdx.x;
   const int inner = heads * vdim;
   const int scan_row = 2 * gn + inner;
-  if (blockIdx.y == 0 && threadIdx.x < heads) {
-    const int h = threadIdx.x;
-    const float dt = softplus_f(proj[(size_t)t * proj_stride + dt_offset + h] + dt_bias[h]);
-    decay[(size_t)t * heads + h] = live ? expf(-expf(a_log[h]) * dt) : 1.f;
+  // the heads whose x channels this block holds (none where it holds only B and C)
+  const int h_lo = c_lo < inner ? c_lo / vdim : 0;
+  const int h_hi = c_lo < inner ? ((c_lo + NT - 1 < inner ? c_lo + NT - 1 : inner - 1) / vdim) : -1;
+  const int nh = h_hi - h_lo + 1;
+  for (int e = threadIdx.x; e < count * nh; e += NT) {
+    const int tt = e / nh, h = h_lo + e - tt * nh;
+    step[tt][h - h_lo] = softplus_f(proj[(size_t)(t0 + tt) * proj_stride + dt_offset + h] + dt_bias[h]);
   }
-  if (c >= channels) return;
-  float sum = bias[c];
-  if (live) {
-    const int i = t - req_indptr[req];  // the token's place in its request's portion
-    float* old = state + (size_t)slot * (taps - 1) * channels;
-    for (int j = 0; j < taps; ++j) {  // ascending j: oldest input first
-      const int back = taps - 1 - j;
-      const float v = i - back >= 0 ? proj[(size_t)(t - back) * proj_stride + xbc_offset + c]
-                                    : old[(size_t)(taps - 1 + i - back) * channels + c];
-      sum = fmaf(weight[(size_t)c * taps + j], v, sum);
-      // a step of single tokens: this thread alone reads and writes the channel's rows of the slot, so it also moves
-      // them up by one (row j - 1 takes the value just read from row j; the last row takes the token's own input)
-      if (update_state && j > 0) old[(size_t)(j - 1) * channels + c] = v;
+  if (blockIdx.y == 0) {  // the decays of all heads, once
+    for (int e = threadIdx.x; e < count * heads; e += NT) {
+      const int tt = e / heads, h = e - tt * heads;
+      const int slot = slots[token_req[t0 + tt]];  // (before the barrier: not from shared memory)
+      const float dt = softplus_f(proj[(size_t)(t0 + tt) * proj_stride + dt_offset + h] + dt_bias[h]);
+      decay[(size_t)(t0 + tt) * heads + h] = slot >= 0 ? expf(-expf(a_log[h]) * dt) : 1.f;
     }
   }
-  const float act = live ? silu_f(sum) : 0.f;
-  if (c < inner) {
-    const int h = c / vdim;
-    const float dt = softplus_f(proj[(size_t)t * proj_stride + dt_offset + h] + dt_bias[h]);
-    x_out[(size_t)t * inner + c] = act;
-    scan_in[(size_t)t * scan_row + 2 * gn + c] = dt * act;
-  } else if (c < inner + gn) {
-    scan_in[(size_t)t * scan_row + gn + (c - inner)] = act;  // B: the scan's k
-  } else {
-    scan_in[(size_t)t * scan_row + (c - inner - gn)] = act;  // C: the scan's q
+  __syncthreads();
+  if (c >= channels) return;
+  float w[MAX_TAPS], win[MAX_TAPS];  // win[j]: the input taps - 1 - j tokens back; win[taps - 1]: the token's own
+#pragma unroll
+  for (int j = 0; j < MAX_TAPS; ++j) {
+    w[j] = j < taps ? weight[(size_t)c * taps + j] : 0.f;
+    win[j] = 0.f;
+  }
+  const float b = bias[c];
+  const int my_head = c < inner ? c / vdim - h_lo : 0;  // where this channel's step size lies in ``step``
+  float own[CONV_TOKENS];  // the tokens' own inputs: all loads of the tile in flight at once
+#pragma unroll
+  for (int tt = 0; tt < CONV_TOKENS; ++tt)
+    own[tt] = tt < count ? proj[(size_t)(t0 + tt) * proj_stride + xbc_offset + c] : 0.f;
+  int prev_req = -1;
+#pragma unroll
+  for (int tt = 0; tt < CONV_TOKENS; ++tt) {
+    if (tt >= count) break;
+    const int t = t0 + tt;
+    const int req = tile_req[tt];
+    const int slot = tile_slot[tt];
+    const bool live = TL_DEBUG_OK(slot >= -1 && slot < max_slots, TL_DEBUG_SLOT, slot) && slot >= 0;
+    float act = 0.f;
+    if (live) {
+      const int i = tile_place[tt];  // the token's place in its request's portion
+      float* old = state + (size_t)slot * (taps - 1) * channels;
+      const float cur = own[tt];
+      if (req == prev_req) {  // the same request as the token before: the inputs slide by one
+#pragma unroll
+        for (int j = 0; j < MAX_TAPS - 1; ++j)
+          if (j < taps - 1) win[j] = win[j + 1];
+      } else {
+#pragma unroll
+        for (int j = 0; j < MAX_TAPS - 1; ++j) {
+          if (j >= taps - 1) continue;
+          const int back = taps - 1 - j;
+          win[j] = i - back >= 0 ? proj[(size_t)(t - back) * proj_stride + xbc_offset + c]
+                                 : old[(size_t)(taps - 1 + i - back) * channels + c];
+        }
+      }
+      float sum = b;
+#pragma unroll
+      for (int j = 0; j < MAX_TAPS; ++j) {  // ascending j: oldest input first
+        if (j >= taps) continue;
+        if (j == taps - 1) win[j] = cur;
+        sum = fmaf(w[j], win[j], sum);
+      }
+      // a step of single tokens: this thread alone reads and writes the channel's rows of the slot, so it also moves
+      // them up by one (the last row takes the token's own input)
+      if (update_state) {
+#pragma unroll
+        for (int j = 1; j < MAX_TAPS; ++j)
+          if (j < taps) old[(size_t)(j - 1) * channels + c] = win[j];
+      }
+      act = silu_f(sum);
+      prev_req = req;
+    } else {
+      prev_req = -1;
+    }
+    if (c < inner) {
+      x_out[(size_t)t * inner + c] = act;
+      scan_in[(size_t)t * scan_row + 2 * gn + c] = step[tt][my_head] * act;
+    } else if (c < inner + gn) {
+      scan_in[(size_t)t * scan_row + gn + (c - inner)] = act;  // B: the scan's k
+    } else {
+      scan_in[(size_t)t * scan_row + (c - inner - gn)] = act;  // C: the scan's q
+    }
   }
 }
 
@@ -237,12 +302,14 @@ int tl_ssm_conv(const float* proj, int proj_stride, int xbc_offset, int dt_offse
                 const int* req_indptr, const int* slots, float* scan_in, float* x_out, float* decay, int tokens,
                 int taps, int heads, int vdim, int gn, int max_slots, int update_state, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (taps < 1 || taps > MAX_TAPS || heads <= 0 || heads > NT || vdim <= 0 || gn <= 0) return TL_ERR_UNSUPPORTED;
+  // few tokens (a step of single tokens): a block a token, so that the tokens run side by side
+  if (taps < 1 || taps > MAX_TAPS || heads <= 0 || vdim <= 0 || gn <= 0) return TL_ERR_UNSUPPORTED;
   const int channels = heads * vdim + 2 * gn;
-  dim3 grid(tokens, (channels + NT - 1) / NT);
+  const int tile = tokens <= 8 * CONV_TOKENS ? 1 : CONV_TOKENS;
+  dim3 grid((tokens + tile - 1) / tile, (channels + NT - 1) / NT);
   tl::launch_kernel(ssm_conv_kernel, grid, NT, 0, stream, proj, proj_stride, xbc_offset, dt_offset, weight, bias, dt_bias,
-                    a_log, (float*)state, token_req, req_indptr, slots, scan_in, x_out, decay, channels, taps, heads, vdim, gn,
-                    max_slots, update_state);
+                    a_log, (float*)state, token_req, req_indptr, slots, scan_in, x_out, decay, tokens, channels, taps, heads,
+                    vdim, gn, max_slots, update_state, tile);
   return TL_LAUNCH_CHECK();
 }
 
