@@ -77,7 +77,11 @@ __device__ __forceinline__ float gated(float g, float u, float limit, float alph
     u = fminf(fmaxf(u, -limit), limit);
     return g / (1.f + __expf(-alpha * g)) * (u + 1.f);
   }
-  if (limit < 0.f) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+  if (limit < 0.f) {  // (the result is rounded to bfloat16: the approximate tanh, 2^-11 relative, is below that)
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return 0.5f * g * (1.f + t) * u;
+  }
   return silu(g) * u;
 }
 

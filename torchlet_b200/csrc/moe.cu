@@ -26,7 +26,7 @@ namespace {
 
 using namespace tl;
 
-constexpr int ROUTE_WARPS = 8;
+constexpr int ROUTE_WARPS = 16;  // router rows taken side by side (8: ten rows and a gate's row took two rounds of loads)
 constexpr int MAX_EXPERTS = 256;
 
 // One router logit by one warp: each lane sums its 32nd of the row in eight independent chains (k = lane,
@@ -127,7 +127,7 @@ __device__ __forceinline__ void choose_experts(float* score, float* pick, const 
 }
 
 // One block per token.  The token's row is staged in shared memory as floats; warp w takes the
-// experts w, w + 8, ...; the first warp then chooses.
+// experts w, w + ROUTE_WARPS, ...; the first warp then chooses.
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ router, int* __restrict__ choice,
