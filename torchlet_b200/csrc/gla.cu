@@ -79,14 +79,16 @@ template <int N> __device__ __forceinline__ void copies_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// One block per (request, head, COLS value channels), KS * COLS threads.  Four lanes share a column of
-// S (value channel j): lane part p keeps the key channels i with (i / 4) % 4 == p, DK / 4 of them
+// One block per (request, head, COLS value channels), KS * COLS threads.  KS (four or eight) lanes share a
+// column of S (value channel j): lane part p keeps the key channels i with (i / 4) % KS == p, DK / KS of them
 // (DK: the key size rounded up to 16, 32, 64, 128 or 256), and the sum over i of a token's S^T q meets
-// by two shuffles.  Every warp reads the same staged q, k, a of CHUNK tokens, STAGES stages deep: while
+// by two or three shuffles.  Every warp reads the same staged q, k, a of CHUNK tokens, STAGES stages deep: while
 // the block walks one chunk, the next three are on their way (a chunk's copies take longer than its
 // arithmetic).  A token costs a block 3 DK / 4 shared-memory reads of 16 bytes a warp, which is what bounds
 // a block of many warps; hence few columns a block, and more blocks.
-constexpr int KS = 4;
+// Lanes that share a column: four, or eight at key sizes from 128 on (a lane's share of the column, and with it the
+// chain of additions a token, stays at most 32 long, and a block has eight warps to hide the chain's waits behind).
+__host__ __device__ constexpr int lanes_a_column(int dk) { return dk >= 128 ? 8 : 4; }
 constexpr int COLS = 32;
 constexpr int STAGES = 4;
 
@@ -96,13 +98,14 @@ constexpr int STAGES = 4;
 // reading q/k head h / (heads / qk_heads); the rows are [ q (qk_heads D) | k (qk_heads D) | v (heads V) | ... ].
 constexpr int DECAY_ROWS = 0, DECAY_HEAD = 1, DECAY_TOKEN = 2;
 template <int DK, bool VEC, int MODE>
-__global__ void __launch_bounds__(KS * COLS)
+__global__ void __launch_bounds__(lanes_a_column(DK) * COLS)
 gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ decay,
                 const int* __restrict__ req_indptr, const int* __restrict__ slots, float* __restrict__ state,
                 float* __restrict__ out, int heads, int qk_heads, int dim, int vdim, int max_slots, float qscale) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
   constexpr bool FIXED = MODE != DECAY_ROWS;  // no decay row is staged
+  constexpr int KS = lanes_a_column(DK);
   constexpr int PER = DK / KS;
   // a staged token: q, k, (a: only where the decay is a row a token), v, the token's decay number.  Without the a
   // row a stage holds twice as many tokens of the larger key sizes, and the walk meets half as many barriers.
@@ -233,6 +236,7 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
       float o = (o0 + o1) + (o2 + o3);
       o += __shfl_xor_sync(0xffffffffu, o, 1);
       o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (KS == 8) o += __shfl_xor_sync(0xffffffffu, o, 4);
       if (on && part == 0) out[(size_t)(base + tt) * hv + h * vdim + col] = o * qscale;
     }
     __syncthreads();  // the stage is free for the chunk after the next
@@ -322,12 +326,11 @@ int tl_gla_scan(const float* proj, int proj_stride, const float* decay, const in
   if (qk_heads <= 0 || heads % qk_heads || decay_mode < 0 || decay_mode > 2) return TL_ERR_UNSUPPORTED;
   const bool fixed_decay = decay_mode != DECAY_ROWS;
   dim3 grid(requests, heads, (vdim + COLS - 1) / COLS);
-  const int threads = KS * COLS;
   const bool vec = dim % 4 == 0 && vdim % 4 == 0 && proj_stride % 4 == 0 && (qk_heads * dim) % 4 == 0 &&
                    (reinterpret_cast<uintptr_t>(proj) & 15) == 0 &&
                    (fixed_decay || (reinterpret_cast<uintptr_t>(decay) & 15) == 0);
 #define TL_SCAN_ONE(DK, VEC, MODE)                                                                                 \
-  tl::launch_kernel(gla_scan_kernel<DK, VEC, MODE>, grid, threads, 0, stream, proj, proj_stride, decay, req_indptr, \
+  tl::launch_kernel(gla_scan_kernel<DK, VEC, MODE>, grid, lanes_a_column(DK) * COLS, 0, stream, proj, proj_stride, decay, req_indptr, \
                     slots, state, out, heads, qk_heads, dim, vdim, max_slots, qscale)
 #define TL_SCAN(DK)                                                                \
   {                                                                                \
